@@ -1,0 +1,239 @@
+"""Generate the golden fixtures in this directory by running the reference
+implementation (nblauch/fovi, pure PyTorch) on CPU, and pin the NumPy oracle to it.
+
+Run once, where a checkout of the reference is available:
+
+    python tests/golden/make_golden.py --reference /path/to/fovi-checkout
+
+Nothing at test/bench time imports the reference; the ``.npz`` files written here
+travel with the repository instead.  All synthetic inputs come from
+``numpy.random.RandomState`` (a frozen bit-stream), so they can be regenerated
+bit-identically anywhere; weights are Kaiming-normal by construction
+(``N(0,1) * sqrt(2 / fan_in)``, fan_in = Cin*V) and are copied into the reference
+layers before their forward is recorded.
+
+What is pinned while generating (the script aborts if any check fails):
+  * oracle.transform_sampling_grid / grid_sample == reference sampler, bit-exact
+  * oracle.knnconv_forward == reference KNNConvLayer.forward, <= 1e-5 relative
+"""
+import argparse
+import importlib.machinery
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle import fovi_oracle as oracle  # noqa: E402
+
+f32 = np.float32
+
+
+def load_reference(root):
+    """Import the reference's hot-path modules without its trainer/CLI dependencies:
+    seed ``sys.modules['fovi']`` with an empty package pointing at the checkout, stub two
+    plotting/mesh modules the hot path never calls, and import ``fovi.arch.knn`` first."""
+    pkg = types.ModuleType("fovi")
+    pkg.__path__ = [os.path.join(root, "fovi")]
+    pkg.__spec__ = importlib.machinery.ModuleSpec("fovi", None, is_package=True)
+    sys.modules["fovi"] = pkg
+    for name in ("trimesh", "skimage", "skimage.measure"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.modules["skimage.measure"].EllipseModel = object
+    sys.modules["skimage"].measure = sys.modules["skimage.measure"]
+    import fovi.arch.knn as knn
+    import fovi.arch.knnvit as knnvit
+    import fovi.sensing.coords as coords
+    import fovi.sensing.retina as retina
+    return knn, retina, coords, knnvit
+
+
+def synth_images(seed, shape):
+    return np.random.RandomState(seed).random_sample(shape).astype(f32)
+
+
+def synth_fixations(seed, B, F, lo=0.25, span=0.5):
+    return (lo + span * np.random.RandomState(seed).random_sample((B, F, 2))).astype(f32)
+
+
+def kaiming_weight(rs, cout, cin, V):
+    return (rs.standard_normal((cout, cin * V)) * np.sqrt(2.0 / (cin * V))).astype(f32)
+
+
+def coords_dict(c, prefix=""):
+    d = {
+        "cartesian": c.cartesian.numpy(), "polar": c.polar.numpy(), "cortical": c.cortical.numpy(),
+        "cartesian_pad": c.cartesian_pad_coords.numpy(), "cortical_pad": c.cortical_pad_coords.numpy(),
+        "resolution": np.int64(c.resolution), "fov": np.float64(c.fov), "cmf_a": np.float64(c.cmf_a),
+    }
+    return {prefix + k: v for k, v in d.items()}
+
+
+def layer_tables(layer):
+    """int32 [K,Nout] pad-token indices, raw indices, uint16 [Nout,K] tap table, V."""
+    tap = oracle.tap_table_from_local_rf(layer.local_rf.numpy())
+    return {
+        "knn_idx": layer.knn_indices.numpy().astype(np.int32),
+        "knn_idx_pad": layer.knn_indices_pad_token.numpy().astype(np.int32),
+        "tap": tap.astype(np.uint16),
+        "V": np.int64(layer.ref_coords.shape[0]),
+        "n_in": np.int64(layer.in_coords.shape[0]),
+    }
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", required=True)
+    args = ap.parse_args()
+    knn, retina, coords, knnvit = load_reference(args.reference)
+    torch.set_grad_enabled(False)
+    save = lambda name, **kw: np.savez_compressed(os.path.join(HERE, name), **kw)  # noqa: E731
+
+    # ------------------------------------------------------------ sensors (geometry fixtures)
+    sensors = {}
+    for tag, a, start in (("a0p5", 0.5, 256), ("a1", 1.0, 256), ("a2p78", 2.78, 224), ("a2p785765", 2.785765, 224), ("a60p94", 60.94, 256)):
+        rt = retina.RetinalTransform(resolution=64, start_res=start, fov=16, cmf_a=a, style="isotropic",
+                                     sampler="grid_bilinear", fixation_size=start, auto_match_cart_resources=1, device="cpu")
+        sensors[tag] = rt
+        c = rt.sampler.coords
+        save(f"sensor_{tag}.npz", sampling_grid=rt.sampler.sampling_grid.numpy()[0, 0], **coords_dict(c))
+        print("sensor", tag, "resolution", rt.resolution, "N", len(c))
+
+    # ------------------------------------------------------------ config 1: sensor + one KNNConv, fp32
+    rt = sensors["a2p78"]
+    x = synth_images(0, (8, 3, 224, 224))
+    y_ref = rt(torch.from_numpy(x), None).numpy()
+    grid = rt.sampler.sampling_grid.numpy()[0, 0]
+    y_or = oracle.retinal_sample(x, grid, None, np.full((8, 2), 224, f32))
+    assert np.array_equal(y_or, y_ref), "sampler oracle is not bit-exact (config 1)"
+    c = rt.sampler.coords
+    layer = knn.KNNConvLayer(3, 64, 49, c, c, device="cpu", ref_frame_side_length=7, bias=False)
+    rs = np.random.RandomState(1)
+    w = kaiming_weight(rs, 64, 3, 49)
+    layer.weight.data.copy_(torch.from_numpy(w))
+    out_ref = layer(torch.from_numpy(y_ref)).numpy()
+    t = layer_tables(layer)
+    out_or = oracle.knnconv_forward(y_ref, t["knn_idx_pad"], t["tap"].astype(np.int64), int(t["V"]), w)
+    e = rel_err(out_or, out_ref)
+    assert e < 1e-5, e
+    e2 = rel_err(oracle.knnconv_forward_closed_form(y_ref, t["knn_idx_pad"], t["tap"].astype(np.int64), int(t["V"]), w), out_ref)
+    assert e2 < 1e-5, e2
+    print("config1 conv oracle rel err", e, e2)
+    save("config1.npz", sampled=y_ref, conv_out_b0=out_ref[0], conv_out_sum=out_ref.astype(np.float64).sum((1, 2)),
+         conv_out_sqsum=(out_ref.astype(np.float64) ** 2).sum((1, 2)), **t)
+
+    # ------------------------------------------------------------ config 2 (small batch): sampler modes
+    B, F = 2, 3
+    x = synth_images(0, (B, 3, 256, 256))
+    fix = synth_fixations(0, B, F)
+    fix_any = synth_fixations(3, B, F, lo=0.0, span=1.0)      # anywhere in the image: many out-of-image taps
+    sizes = np.array([[[256, 256], [192, 160], [300, 280]]] * B, f32)   # per-fixation (h, w)
+    out = {"fix": fix, "fix_any": fix_any, "sizes": sizes}
+    for tag in ("a1", "a2p78", "a60p94"):
+        rt = sensors[tag]
+        grid = rt.sampler.sampling_grid.numpy()[0, 0]
+        fs = rt.fixation_size                                 # default fixation size of this sensor (224 or 256)
+        out[f"{tag}_default_size"] = np.int64(fs)
+        for mode in ("bilinear", "nearest"):
+            rt.sampler.mode = mode
+            for fname, fx in (("near", fix), ("any", fix_any)):
+                ys, ysz, yb = [], [], []
+                for f in range(F):
+                    ys.append(rt(torch.from_numpy(x), torch.from_numpy(fx[:, f])).numpy())
+                    ysz.append(rt(torch.from_numpy(x), torch.from_numpy(fx[:, f]), fixation_size=torch.from_numpy(sizes[:, f])).numpy())
+                    g = coords.transform_sampling_grid(rt.sampler.sampling_grid, torch.from_numpy(fx[:, f]), torch.from_numpy(np.full((B, 2), fs, np.int64)), (256, 256))
+                    yb.append(torch.nn.functional.grid_sample(torch.from_numpy(x), g, mode=mode, padding_mode="border", align_corners=False).squeeze(2).numpy())
+                ys, ysz, yb = np.stack(ys, 1), np.stack(ysz, 1), np.stack(yb, 1)
+                o = oracle.retinal_sample(x, grid, fx, np.full((B, F, 2), fs, f32), mode, "zeros")
+                assert np.array_equal(o, ys), (tag, mode, fname, "zeros", np.abs(o - ys).max())
+                o = oracle.retinal_sample(x, grid, fx, sizes, mode, "zeros")
+                assert np.array_equal(o, ysz), (tag, mode, fname, "sizes", np.abs(o - ysz).max())
+                o = oracle.retinal_sample(x, grid, fx, np.full((B, F, 2), fs, f32), mode, "border")
+                assert np.array_equal(o, yb), (tag, mode, fname, "border", np.abs(o - yb).max())
+                out[f"{tag}_{mode}_{fname}_zeros"] = ys
+                if fname == "near":          # all variants are checked above; a subset is stored to keep the fixture small
+                    out[f"{tag}_{mode}_{fname}_sizes"] = ysz
+                else:
+                    out[f"{tag}_{mode}_{fname}_border"] = yb
+            rt.sampler.mode = "bilinear"
+        print("config2 sampler oracle bit-exact for", tag)
+    save("config2_small.npz", **out)
+
+    # ------------------------------------------------------------ config 3: AlexNet-shaped KNNConv stack
+    fov, a = 16, 1.0
+    chans, strides, ks = [3, 64, 192, 384, 256, 256], [2, 2, 1, 1, 1], [121, 25, 9, 9, 9]
+    in_res, cart_res = coords.auto_match_num_coords(fov, a, 64, "isotropic", 1, "cpu", quiet=True)
+    rs = np.random.RandomState(1)
+    layers, tables, in_coords = [], {}, None
+    for i in range(5):
+        ic, oc, out_cart = knn.get_in_out_coords(in_res, fov, a, strides[i], style="isotropic", auto_match_cart_resources=1, in_cart_res=cart_res, device="cpu")
+        side = int(np.ceil(2 * np.sqrt(ks[i])))
+        L = knn.KNNConvLayer(chans[i], chans[i + 1], ks[i], ic, oc, device="cpu", ref_frame_side_length=side, bias=True)
+        w = kaiming_weight(rs, chans[i + 1], chans[i], side * side)
+        L.weight.data.copy_(torch.from_numpy(w))
+        L.bias.data.zero_()
+        layers.append((L, w))
+        for k_, v_ in layer_tables(L).items():
+            tables[f"l{i}_{k_}"] = v_
+        tables.update(coords_dict(ic, f"l{i}_in_"))
+        tables[f"l{i}_out_resolution"] = np.int64(oc.resolution)
+        print(f"config3 layer {i}: Nin {len(ic)} Nout {len(oc)} K {L._k} V {side*side} pad {float(L.knn_indices_pad_mask.float().mean()):.4f}")
+        in_res, cart_res = oc.resolution, out_cart
+    tables.update(coords_dict(oc, "l5_in_"))
+    xb = synth_images(0, (2, 3, int(tables["l0_n_in"])))
+    h = torch.from_numpy(xb)
+    acts = {}
+    ho = xb
+    for i, (L, w) in enumerate(layers):
+        h = L(h)
+        ho = oracle.knnconv_forward(ho, tables[f"l{i}_knn_idx_pad"], tables[f"l{i}_tap"].astype(np.int64), int(tables[f"l{i}_V"]), w, np.zeros(chans[i + 1], f32))
+        if i < 4:
+            h = torch.relu(h)
+            ho = np.maximum(ho, 0)
+        acts[f"act{i}"] = h.numpy()
+        e = rel_err(ho, h.numpy())
+        assert e < 1e-5, (i, e)
+    print("config3 stack oracle ok")
+    save("config3_tables.npz", **tables)
+    save("config3_acts_b2.npz", **acts)
+
+    # ------------------------------------------------------------ config 4: foveated patch embedding 3 -> 384
+    for tag, patch in (("p8", 8), ("p4", 4)):
+        pe = knnvit.KNNPartitioningPatchEmbedding(3, 384, in_res=64, fov=16, cmf_a=2.78, in_cart_res=64, cart_patch_size=patch,
+                                                  ref_frame_side_length=16, max_coord_val="auto", sample_cortex=True, bias=True,
+                                                  transposed=True, device="cpu")
+        t = layer_tables(pe)
+        V = int(t["V"])
+        w = kaiming_weight(np.random.RandomState(1), 384, 3, V)
+        bvec = (0.1 * np.random.RandomState(2).standard_normal(384)).astype(f32)
+        pe.weight.data.copy_(torch.from_numpy(w)); pe.bias.data.copy_(torch.from_numpy(bvec))
+        xb = synth_images(0, (2, 3, int(t["n_in"])))
+        o_ref = pe(torch.from_numpy(xb)).numpy()
+        o = oracle.knnconv_forward(xb, t["knn_idx_pad"], t["tap"].astype(np.int64), V, w, bvec)
+        e = rel_err(o, o_ref)
+        assert e < 1e-5, e
+        print(f"config4 patch-embed {tag}: Nin {int(t['n_in'])} tokens {o_ref.shape[-1]} K {pe._k} V {V} err {e:.2e}")
+        save(f"config4_patch_embed_{tag}.npz", out_b2=o_ref, in_cartesian=pe.in_coords.cartesian.numpy(), out_cartesian=pe.out_coords.cartesian.numpy(),
+             out_cortical=pe.out_coords.cortical.numpy(), **t)
+
+    # ------------------------------------------------------------ max pooling (next-row fixture)
+    c = sensors["a0p5"].sampler.coords
+    ic, oc, _ = knn.get_in_out_coords(c.resolution, 16, 0.5, 2, style="isotropic", auto_match_cart_resources=1, in_cart_res=64, device="cpu", in_coords=c)
+    pool = knn.KNNPoolingLayer(9, ic, oc, mode="max", device="cpu")
+    xb = synth_images(5, (2, 4, len(ic))) - f32(0.5)
+    p_ref = pool(torch.from_numpy(xb)).numpy()
+    idxp = pool.knn_indices_pad_token.numpy().astype(np.int32)
+    assert np.array_equal(oracle.knn_pool_max(xb, idxp), p_ref)
+    save("pool_a0p5.npz", knn_idx_pad=idxp, out=p_ref, n_in=np.int64(len(ic)), n_out=np.int64(len(oc)))
+    print("point counts a=0.5 chain:", len(ic), len(oc))
+
+
+if __name__ == "__main__":
+    main()
