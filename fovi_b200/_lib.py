@@ -1,0 +1,56 @@
+"""ctypes binding of ``libfovi_b200.so`` (the C ABI declared in ``include/fovi_b200.h``).
+
+There is no fallback: if the shared object is missing or a symbol cannot be bound, importing
+this module raises.  Build it with ``python -m fovi_b200.build``.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libfovi_b200.so")
+
+# name -> (restype, argtypes); must list every symbol the header declares.
+_P = C.c_void_p
+SIGNATURES = {
+    "fovi_status_string": (C.c_char_p, [C.c_int]),
+    "fovi_last_cuda_error": (C.c_char_p, []),
+    "fovi_version": (C.c_char_p, []),
+    "fovi_sampler_plan_create": (C.c_int, [_P, C.c_int, C.POINTER(_P)]),
+    "fovi_sampler_plan_destroy": (None, [_P]),
+    "fovi_sampler_plan_num_points": (C.c_int, [_P]),
+    "fovi_sample_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), _P, _P,
+                                      C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_knnconv_plan_create": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
+    "fovi_knnconv_plan_destroy": (None, [_P]),
+    "fovi_knnconv_cin_packed": (C.c_int, [_P]),
+    "fovi_knnconv_nnz": (C.c_int64, [_P]),
+    "fovi_knnconv_pack_weights": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, _P]),
+    "fovi_knnconv_packed_weight_bytes": (C.c_int64, [_P, C.c_int]),
+    "fovi_pack_points": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_int, _P]),
+    "fovi_knnconv_forward": (C.c_int, [_P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_knnconv_forward_f32": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_knnconv_check": (C.c_int, [_P, _P]),
+    "fovi_launch_count": (C.c_int64, []),
+}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(f"{LIB_PATH} not found: the CUDA library has not been built (run `python -m fovi_b200.build`); "
+                      "fovi_b200 has no CPU or PyTorch fallback")
+
+lib = C.CDLL(LIB_PATH)
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)          # AttributeError if the library lacks a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+class FoviError(RuntimeError):
+    def __init__(self, status, where):
+        self.status = status
+        detail = lib.fovi_last_cuda_error().decode() if status in (4, 6) else ""
+        super().__init__(f"{where}: {lib.fovi_status_string(status).decode()}" + (f" ({detail})" if detail else ""))
+
+
+def check(status, where):
+    if status != 0:
+        raise FoviError(status, where)

@@ -1,0 +1,183 @@
+// KNNConv: plan construction, operand packing and the exact float32 (CUDA-core) forward.
+#include <vector>
+
+#include "knnconv_plan.cuh"
+
+namespace {
+
+// W [c_out, c_in*V] (c-major, v-minor)  ->  slabs [V, c_out, cp]
+template <typename TW, typename TD>
+__global__ void pack_weights_kernel(const TW* __restrict__ W, TD* __restrict__ dst, int V, int c_out, int c_in, int cp) {
+  const long long total = (long long)V * c_out * cp;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % cp);
+    const int o = (int)((i / cp) % c_out);
+    const int v = (int)(i / ((long long)cp * c_out));
+    const float w = c < c_in ? ld_as_float(W + ((long long)o * c_in + c) * V + v) : 0.f;
+    dst[i] = from_float<TD>(w);
+  }
+}
+
+// X [B,C,N] -> [B,N,cp] bf16, transposing 32x32 tiles through shared memory.
+template <typename TX>
+__global__ void pack_points_kernel(const TX* __restrict__ x, __nv_bfloat16* __restrict__ dst, int C, int N, int cp) {
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  const int n0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const TX* xb = x + (long long)b * C * N;
+  __nv_bfloat16* db = dst + (long long)b * N * cp;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r, n = n0 + threadIdx.x;
+    tile[r][threadIdx.x] = (c < C && n < N) ? ld_as_float(xb + (long long)c * N + n) : 0.f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int n = n0 + r, c = c0 + threadIdx.x;
+    if (n < N && c < cp) db[(long long)n * cp + c] = __float2bfloat16_rn(tile[threadIdx.x][r]);
+  }
+}
+
+// Exact float32 forward.  One CTA: one output point, BT batch rows, all output channels.
+template <typename TX, bool X_BNC, bool Y_BNC>
+__global__ void __launch_bounds__(128) knnconv_f32_kernel(const TX* __restrict__ X, const float* __restrict__ Wt,
+                                                          const float* __restrict__ bias, float* __restrict__ Y,
+                                                          const int* __restrict__ nbr_idx, const uint16_t* __restrict__ nbr_tap,
+                                                          const int* __restrict__ nbr_cnt, int kp, int B, int n_in, int n_out,
+                                                          int c_in, int c_out, int cp, int relu, int BT) {
+  const int n = blockIdx.x;
+  const int b0 = blockIdx.y * BT;
+  const int cnt = nbr_cnt[n];
+  const int* idx = nbr_idx + (long long)n * kp;
+  const uint16_t* tp = nbr_tap + (long long)n * kp;
+  const int bt = min(BT, B - b0);
+  for (int p = threadIdx.x; p < bt * c_out; p += blockDim.x) {
+    const int o = p % c_out, b = b0 + p / c_out;
+    float acc = 0.f;
+    for (int k = 0; k < cnt; ++k) {
+      const int j = idx[k];
+      const float* w = Wt + ((long long)tp[k] * c_out + o) * cp;
+      for (int c = 0; c < c_in; ++c) {
+        const float xv = X_BNC ? ld_as_float(X + ((long long)b * n_in + j) * c_in + c)
+                               : ld_as_float(X + ((long long)b * c_in + c) * n_in + j);
+        acc = fmaf(xv, __ldg(w + c), acc);
+      }
+    }
+    if (bias) acc += __ldg(bias + o);
+    if (relu) acc = fmaxf(acc, 0.f);
+    if (Y_BNC) Y[((long long)b * n_out + n) * c_out + o] = acc;
+    else Y[((long long)b * c_out + o) * n_out + n] = acc;
+  }
+}
+
+}  // namespace
+
+extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16_t* tap, int n_in, int n_out, int K, int V,
+                                        int c_in, int c_out, fovi_knnconv_plan** out) {
+  if (!knn_idx_pad || !tap || !out) return FOVI_ERR_INVALID_ARGUMENT;
+  if (n_in <= 0 || n_out <= 0 || K <= 0 || V <= 0 || c_in <= 0 || c_out <= 0 || V > 65535) return FOVI_ERR_INVALID_ARGUMENT;
+  const int kp = (K + 7) / 8 * 8;
+  std::vector<int> idx((size_t)n_out * kp, n_in), cnt(n_out, 0);
+  std::vector<uint16_t> tp((size_t)n_out * kp, 0);
+  int64_t nnz = 0;
+  for (int n = 0; n < n_out; ++n) {
+    int m = 0;
+    for (int k = 0; k < K; ++k) {
+      const int j = knn_idx_pad[(size_t)k * n_out + n];
+      const int t = tap[(size_t)n * K + k];
+      if (j < 0 || j > n_in || t >= V) return FOVI_ERR_TABLE_RANGE;
+      if (j == n_in) continue;  // pad neighbour: contributes nothing
+      idx[(size_t)n * kp + m] = j;
+      tp[(size_t)n * kp + m] = (uint16_t)t;
+      ++m;
+    }
+    cnt[n] = m;
+    nnz += m;
+  }
+  auto* p = new fovi_knnconv_plan();
+  p->n_in = n_in; p->n_out = n_out; p->K = K; p->V = V; p->c_in = c_in; p->c_out = c_out; p->kp = kp; p->nnz = nnz;
+  p->cin_packed = (c_in % 64 == 0) ? c_in : (c_in + 7) / 8 * 8;
+  cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess) e = cudaMalloc(&p->nbr_idx, sizeof(int) * idx.size());
+  if (e == cudaSuccess) e = cudaMalloc(&p->nbr_tap, sizeof(uint16_t) * tp.size());
+  if (e == cudaSuccess) e = cudaMalloc(&p->nbr_cnt, sizeof(int) * n_out);
+  if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemcpy(p->nbr_idx, idx.data(), sizeof(int) * idx.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->nbr_tap, tp.data(), sizeof(uint16_t) * tp.size(), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(p->nbr_cnt, cnt.data(), sizeof(int) * n_out, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    fovi_knnconv_plan_destroy(p);
+    return fovi::cuda_fail(e, "fovi_knnconv_plan_create");
+  }
+  *out = p;
+  return FOVI_OK;
+}
+
+extern "C" void fovi_knnconv_plan_destroy(fovi_knnconv_plan* p) {
+  if (!p) return;
+  if (p->nbr_idx) cudaFree(p->nbr_idx);
+  if (p->nbr_tap) cudaFree(p->nbr_tap);
+  if (p->nbr_cnt) cudaFree(p->nbr_cnt);
+  if (p->status) cudaFree(p->status);
+  delete p;
+}
+
+extern "C" int fovi_knnconv_cin_packed(const fovi_knnconv_plan* p) { return p ? p->cin_packed : -1; }
+extern "C" int64_t fovi_knnconv_nnz(const fovi_knnconv_plan* p) { return p ? p->nnz : -1; }
+
+extern "C" int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* p, int dst_dtype) {
+  if (!p || !fovi::valid_dtype(dst_dtype)) return -1;
+  return (int64_t)p->V * p->c_out * p->cin_packed * (int64_t)fovi::dtype_size(dst_dtype);
+}
+
+extern "C" int fovi_knnconv_pack_weights(const fovi_knnconv_plan* p, const void* W, int w_dtype, void* dst, int dst_dtype,
+                                         void* stream) {
+  if (!p || !W || !dst || !fovi::valid_dtype(w_dtype) || !fovi::valid_dtype(dst_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long total = (long long)p->V * p->c_out * p->cin_packed;
+  const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+#define PACK(TW, TD) \
+  pack_weights_kernel<TW, TD><<<grid, 256, 0, st>>>((const TW*)W, (TD*)dst, p->V, p->c_out, p->c_in, p->cin_packed)
+  if (w_dtype == FOVI_F32 && dst_dtype == FOVI_F32) PACK(float, float);
+  else if (w_dtype == FOVI_F32 && dst_dtype == FOVI_BF16) PACK(float, __nv_bfloat16);
+  else if (w_dtype == FOVI_BF16 && dst_dtype == FOVI_F32) PACK(__nv_bfloat16, float);
+  else PACK(__nv_bfloat16, __nv_bfloat16);
+#undef PACK
+  return fovi::after_launch("pack_weights_kernel");
+}
+
+extern "C" int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, void* stream) {
+  if (!x || !dst || !fovi::valid_dtype(x_dtype) || B < 0 || C <= 0 || N <= 0 || cp < C || cp % 8) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;
+  if (B > 65535) return FOVI_ERR_UNSUPPORTED;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid((N + 31) / 32, (cp + 31) / 32, B), block(32, 8);
+  if (x_dtype == FOVI_F32) pack_points_kernel<float><<<grid, block, 0, st>>>((const float*)x, (__nv_bfloat16*)dst, C, N, cp);
+  else pack_points_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)dst, C, N, cp);
+  return fovi::after_launch("pack_points_kernel");
+}
+
+extern "C" int fovi_knnconv_forward_f32(const fovi_knnconv_plan* p, const void* X, int x_dtype, int x_layout, const float* Wt,
+                                        const float* bias, float* Y, int y_layout, int B, int relu, void* stream) {
+  if (!p || !X || !Wt || !Y || !fovi::valid_dtype(x_dtype) || B < 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if ((x_layout != FOVI_ACT_BCN && x_layout != FOVI_ACT_BNC) || (y_layout != FOVI_ACT_BCN && y_layout != FOVI_ACT_BNC))
+    return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int BT = 4;
+  if ((B + BT - 1) / BT > 65535) return FOVI_ERR_UNSUPPORTED;
+  dim3 grid(p->n_out, (B + BT - 1) / BT);
+#define RUN(TX, XL, YL)                                                                                                   \
+  knnconv_f32_kernel<TX, XL, YL><<<grid, 128, 0, st>>>((const TX*)X, Wt, bias, Y, p->nbr_idx, p->nbr_tap, p->nbr_cnt, p->kp, B, \
+                                                       p->n_in, p->n_out, p->c_in, p->c_out, p->cin_packed, relu, BT)
+  const bool xb = x_layout == FOVI_ACT_BNC, yb = y_layout == FOVI_ACT_BNC;
+  if (x_dtype == FOVI_F32) {
+    if (xb && yb) RUN(float, true, true); else if (xb) RUN(float, true, false);
+    else if (yb) RUN(float, false, true); else RUN(float, false, false);
+  } else {
+    if (xb && yb) RUN(__nv_bfloat16, true, true); else if (xb) RUN(__nv_bfloat16, true, false);
+    else if (yb) RUN(__nv_bfloat16, false, true); else RUN(__nv_bfloat16, false, false);
+  }
+#undef RUN
+  return fovi::after_launch("knnconv_f32_kernel");
+}

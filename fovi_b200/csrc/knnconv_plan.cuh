@@ -1,0 +1,17 @@
+// Plan object shared by the KNNConv translation units.
+#pragma once
+#include "common.cuh"
+
+struct fovi_knnconv_plan {
+  int n_in = 0, n_out = 0, K = 0, V = 0, c_in = 0, c_out = 0;
+  int cin_packed = 0;  // channel count of the packed bf16/f32 operands
+  int kp = 0;          // compacted neighbour-list pitch: K rounded up to a multiple of 8
+  int device = -1;
+  int64_t nnz = 0;     // non-pad (n,k) entries
+  // Compacted per-output-point neighbour lists: entries [0,cnt[n]) are the non-pad neighbours in
+  // their original order; the rest of the row holds idx = n_in (reads as zero), tap = 0.
+  int* nbr_idx = nullptr;       // [n_out, kp]
+  uint16_t* nbr_tap = nullptr;  // [n_out, kp]
+  int* nbr_cnt = nullptr;       // [n_out]
+  int* status = nullptr;        // device word written by a tensor-core kernel whose wait gave up
+};

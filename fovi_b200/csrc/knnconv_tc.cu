@@ -1,0 +1,436 @@
+// KNNConv on the 5th-generation tensor cores (tcgen05 MMA, accumulators in tensor memory).
+//
+//   out[b, n, o] = bias[o] + sum_k sum_c X[b, idx[n,k], c] * Wt[tap[n,k]][o][c]
+//
+// For one output point n the sum over (k, c) is an ordinary GEMM whose M dimension is the
+// batch: D[128 batch rows, c_out tile] += A_k[128, c] * B_k[c, c_out tile], where
+//   A_k = X[b0:b0+128, idx[n,k], :]   a strided 2-D box of the channels-last activations,
+//   B_k = Wt[tap[n,k]]                one slab of the tap-major packed weights.
+// Both operands are therefore plain tiled TMA boxes chosen by the neighbour table, no element
+// gather is needed, pad neighbours are skipped (the plan compacted them away) and the V/K-fold
+// zero work of a one-hot scatter formulation never exists.
+//
+// CTA = 6 warps, persistent over work items (batch tile, output point, c_out tile):
+//   warp 0      producer: stages the item's (idx, tap) list in shared memory, then one lane
+//               issues the TMA loads into a ring of shared-memory stages;
+//   warp 1      one lane issues tcgen05.mma (M=128, N=c_out tile, K=16) and commits to
+//               mbarriers; the warp owns the tensor-memory allocation;
+//   warps 2-5   epilogue: tcgen05.ld the finished accumulator (double-buffered in tensor
+//               memory so the next item's MMAs overlap), add bias, ReLU, convert, store.
+//
+// Two operand modes:
+//   C64  channels packed to a multiple of 64: a stage is one 64-channel chunk of one neighbour,
+//        128-byte-swizzled K-major tiles (4 MMAs of K=16 per stage);
+//   C8   any multiple of 8 channels (the 3-channel first layer packs to 8): a stage is eight
+//        (neighbour, 8-channel chunk) boxes of 16-byte rows in the un-swizzled core-matrix
+//        layout; one MMA (K=16) consumes two boxes.  Tail boxes read the out-of-range point
+//        index n_in, which TMA fills with zeros.
+//
+// Every wait is bounded: a wait that gives up raises a CTA-wide abort flag and a status word in
+// global memory (read back by fovi_knnconv_check); all roles then drain and leave normally, the
+// tensor memory is freed and the context stays usable.
+#include <cuda.h>
+
+#include "knnconv_plan.cuh"
+
+namespace {
+
+constexpr int BM = 128;            // batch rows per tile (UMMA M)
+constexpr int MAX_STAGES = 8;
+constexpr uint32_t A_STAGE_BYTES = 16384;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait attempts before giving up
+
+struct TcArgs {
+  const int* nbr_idx; const uint16_t* nbr_tap; const int* nbr_cnt;
+  const float* bias; void* Y; int* status;
+  int kp, B, n_in, n_out, c_out, cp;
+  int ct, n_ct, n_mt, nstage, relu, y_f32, total_items;
+  uint32_t stage_bytes, table_bytes;
+};
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (K-major operand).  layout: 0 = no swizzle, 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+// Shared-memory header at the 1024-aligned base of the dynamic allocation.
+struct SmemHeader {
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <bool C64>
+__global__ void __launch_bounds__(192, 1)
+fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* basep = smem_raw + (base - raw);
+  SmemHeader* hdr = reinterpret_cast<SmemHeader*>(basep);
+  int* tb_idx = reinterpret_cast<int*>(basep + 1024);
+  uint16_t* tb_tap = reinterpret_cast<uint16_t*>(basep + 1024 + (size_t)a.kp * 4);
+  const uint32_t stages0 = base + 1024u + a.table_bytes;  // 1024-aligned
+  volatile int* abort_flag = &hdr->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t b_stage_off = A_STAGE_BYTES;
+  const int chunks = C64 ? a.cp / 64 : a.cp / 8;  // operand boxes per neighbour
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.nstage; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&hdr->acc_full[i]), 1); mbar_init(smem_u32(&hdr->acc_empty[i]), 128); }
+    mbar_init(smem_u32(&hdr->drain), 1);
+    hdr->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // allocate all 512 tensor-memory columns: two accumulators of up to 256
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&hdr->tmem_base)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = hdr->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    uint32_t s = 0, ph = 0;
+    uint32_t issued = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
+      const int ctile = item % a.n_ct;
+      const int t = item / a.n_ct;
+      const int n = t % a.n_out, mt = t / a.n_out;
+      const int cnt = __ldg(a.nbr_cnt + n);
+      __syncwarp();
+      for (int k = lane; k < a.kp; k += 32) {
+        tb_idx[k] = __ldg(a.nbr_idx + (size_t)n * a.kp + k);
+        tb_tap[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const int m0 = mt * BM, o0 = ctile * a.ct;
+        if (C64) {
+          const int steps = cnt * chunks;
+          int k = 0, cc = 0;
+          for (int st = 0; st < steps; ++st) {
+            const uint32_t full = smem_u32(&hdr->full[s]);
+            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+            mbar_expect_tx(full, a.stage_bytes);
+            const uint32_t sa = stages0 + s * a.stage_bytes;
+            tma_load_3d(sa, &tmA, full, cc * 64, tb_idx[k], m0);
+            tma_load_3d(sa + b_stage_off, &tmB, full, cc * 64, o0, tb_tap[k]);
+            ++issued;
+            if (++cc == chunks) { cc = 0; ++k; }
+            if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+          }
+        } else {
+          const int boxes = cnt * chunks;
+          const int steps = (boxes + 7) / 8;
+          int k = 0, cc = 0;
+          for (int st = 0; st < steps; ++st) {
+            const uint32_t full = smem_u32(&hdr->full[s]);
+            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+            mbar_expect_tx(full, a.stage_bytes);
+            const uint32_t sa = stages0 + s * a.stage_bytes;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const bool live = k < cnt;
+              tma_load_3d(sa + j * 2048u, &tmA, full, cc * 8, live ? tb_idx[k] : a.n_in, m0);
+              tma_load_3d(sa + b_stage_off + j * (uint32_t)a.ct * 16u, &tmB, full, cc * 8, o0, live ? tb_tap[k] : 0);
+              if (++cc == chunks) { cc = 0; ++k; }
+            }
+            ++issued;
+            if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    }
+    if (lane == 0 && *abort_flag) {
+      // Drain: wait (bounded, errors ignored) for the loads this thread armed and nobody consumed.
+      const uint32_t back = issued < (uint32_t)a.nstage ? issued : (uint32_t)a.nstage;
+      uint32_t ds = s, dph = ph;
+      for (uint32_t i = 0; i < back; ++i) {
+        if (ds == 0) { ds = a.nstage - 1; dph ^= 1u; } else { --ds; }
+        for (uint32_t it = 0; it < (1u << 16); ++it)
+          if (mbar_try_wait(smem_u32(&hdr->full[ds]), dph)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.ct >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      uint32_t s = 0, ph = 0, acc = 0, aph = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
+        const int n = (item / a.n_ct) % a.n_out;
+        const int cnt = __ldg(a.nbr_cnt + n);
+        const int steps = C64 ? cnt * chunks : (cnt * chunks + 7) / 8;
+        if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + acc * 256u;
+        for (int st = 0; st < steps; ++st) {
+          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, a.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = stages0 + s * a.stage_bytes, sb = sa + b_stage_off;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            uint64_t da, db;
+            if (C64) {
+              da = smem_desc(sa + kk * 32u, 16u, 1024u, 2u);
+              db = smem_desc(sb + kk * 32u, 16u, 1024u, 2u);
+            } else {
+              da = smem_desc(sa + kk * 4096u, 2048u, 128u, 0u);
+              db = smem_desc(sb + kk * 2u * (uint32_t)a.ct * 16u, (uint32_t)a.ct * 16u, 128u, 0u);
+            }
+            tc_mma_bf16(d_tmem, da, db, idesc, (st | kk) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&hdr->empty[s]));  // frees the stage once these MMAs have read it
+          if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&hdr->acc_full[acc]));  // accumulator complete
+        if (++acc == 2) { acc = 0; aph ^= 1u; }
+      }
+      if (*abort_flag) {  // make sure no MMA is still reading shared memory / writing tensor memory
+        tc_commit(smem_u32(&hdr->drain));
+        for (uint32_t it = 0; it < (1u << 20); ++it)
+          if (mbar_try_wait(smem_u32(&hdr->drain), 0)) break;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    uint32_t acc = 0, aph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
+      const int ctile = item % a.n_ct;
+      const int t = item / a.n_ct;
+      const int n = t % a.n_out, mt = t / a.n_out;
+      const int cnt = __ldg(a.nbr_cnt + n);
+      if (!mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mt * BM + q * 32 + lane;
+      const int o0 = ctile * a.ct;
+      const size_t y_off = ((size_t)row * a.n_out + n) * a.c_out + o0;
+      const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + acc * 256u;
+      for (int c0 = 0; c0 < a.ct; c0 += 16) {
+        uint32_t r[16];
+        tc_ld16(t_base + c0, r);
+        tc_ld_wait();
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float x = cnt > 0 ? __uint_as_float(r[i]) : 0.f;
+          if (a.bias) x += __ldg(a.bias + o0 + c0 + i);
+          v[i] = a.relu ? fmaxf(x, 0.f) : x;
+        }
+        if (row < a.B) {
+          if (a.y_f32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.Y) + y_off + c0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          } else {
+            uint32_t pk[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+              pk[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + y_off + c0);
+            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&hdr->acc_empty[acc]));
+      if (++acc == 2) { acc = 0; aph ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+              uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { fovi::g_last_cuda_error = "cuTensorMapEncodeTiled entry point not available"; return FOVI_ERR_CUDA; }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fovi::g_last_cuda_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);
+    return FOVI_ERR_CUDA;
+  }
+  return FOVI_OK;
+}
+
+// Largest c_out tile <= 256 that divides c_out and is a multiple of 16.
+int pick_cout_tile(int c_out) {
+  for (int n_ct = 1; n_ct <= c_out / 16; ++n_ct) {
+    if (c_out % n_ct) continue;
+    const int ct = c_out / n_ct;
+    if (ct <= 256 && ct % 16 == 0) return ct;
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
+                                    int y_dtype, int B, int relu, void* stream) {
+  if (!p || !X || !Wt || !Y || B < 0 || !fovi::valid_dtype(y_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;
+  if (p->c_out % 16) return FOVI_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Wt) | reinterpret_cast<uintptr_t>(Y)) & 15) return FOVI_ERR_ALIGNMENT;
+  const int ct = pick_cout_tile(p->c_out);
+  if (!ct) return FOVI_ERR_UNSUPPORTED;
+  const int cp = p->cin_packed;
+  const bool c64 = cp % 64 == 0;
+
+  TcArgs a;
+  a.nbr_idx = p->nbr_idx; a.nbr_tap = p->nbr_tap; a.nbr_cnt = p->nbr_cnt;
+  a.bias = bias; a.Y = Y; a.status = p->status;
+  a.kp = p->kp; a.B = B; a.n_in = p->n_in; a.n_out = p->n_out; a.c_out = p->c_out; a.cp = cp;
+  a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;
+  a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
+  const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
+  if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
+  a.total_items = (int)items;
+  a.stage_bytes = A_STAGE_BYTES + (uint32_t)ct * 128u;
+  a.table_bytes = ((uint32_t)p->kp * 6u + 1023u) & ~1023u;
+  const uint32_t budget = 220u * 1024u - 2048u - a.table_bytes;
+  a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
+  if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;
+  const size_t smem = 1024 /*align slack*/ + 1024 /*header*/ + a.table_bytes + (size_t)a.nstage * a.stage_bytes;
+
+  CUtensorMap tmA, tmB;
+  const uint32_t kc = c64 ? 64 : 8;
+  int rc = encode_3d(&tmA, X, (uint64_t)cp, (uint64_t)p->n_in, (uint64_t)B, (uint64_t)cp * 2, (uint64_t)p->n_in * cp * 2, kc, 1, BM, c64);
+  if (rc) return rc;
+  rc = encode_3d(&tmB, Wt, (uint64_t)cp, (uint64_t)p->c_out, (uint64_t)p->V, (uint64_t)cp * 2, (uint64_t)p->c_out * cp * 2, kc, (uint32_t)ct, 1, c64);
+  if (rc) return rc;
+
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = std::min(a.total_items, fovi::sm_count());
+  if (c64) {
+    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fovi_knnconv_tc_kernel<true><<<grid, 192, smem, st>>>(tmA, tmB, a);
+  } else {
+    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fovi_knnconv_tc_kernel<false><<<grid, 192, smem, st>>>(tmA, tmB, a);
+  }
+  return fovi::after_launch("fovi_knnconv_tc_kernel");
+}
+
+extern "C" int fovi_knnconv_check(fovi_knnconv_plan* p, void* stream) {
+  if (!p) return FOVI_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int h = 0;
+  FOVI_CUDA(cudaMemcpyAsync(&h, p->status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  FOVI_CUDA(cudaStreamSynchronize(st));
+  if (h != 0) {
+    FOVI_CUDA(cudaMemsetAsync(p->status, 0, sizeof(int), st));
+    FOVI_CUDA(cudaStreamSynchronize(st));
+    fovi::g_last_cuda_error = "tensor-core KNNConv kernel gave up on wait site " + std::to_string(h);
+    return FOVI_ERR_DEVICE_TIMEOUT;
+  }
+  return FOVI_OK;
+}

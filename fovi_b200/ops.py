@@ -1,0 +1,169 @@
+"""Tensor-level wrappers over the C ABI: plans own device tables, functions take torch CUDA
+tensors, pass raw pointers and the current stream, and allocate outputs with torch."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from ._lib import lib, check
+
+F32, BF16 = 0, 1
+NEAREST, BILINEAR = 0, 1
+PAD_ZEROS, PAD_BORDER = 0, 1
+OUT_BFCN, OUT_FBCN, OUT_BFNC, OUT_FBNC = 0, 1, 2, 3
+ACT_BCN, ACT_BNC = 0, 1
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _dt(t):
+    try:
+        return _DT[t]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t}: the kernels take float32 or bfloat16") from None
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr())
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("fovi_b200 kernels need CUDA tensors; there is no CPU path")
+
+
+class SamplerPlan:
+    """Device copy of a sensor's sampling grid in visiting order (fovi_sampler_plan)."""
+
+    def __init__(self, grid_xy, device=None):
+        g = np.ascontiguousarray(np.asarray(grid_xy, np.float32).reshape(-1, 2))
+        self.n_points = g.shape[0]
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib.fovi_sampler_plan_create(g.ctypes.data_as(C.c_void_p), self.n_points, C.byref(h)), "fovi_sampler_plan_create")
+        self._h = h
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib.fovi_sampler_plan_destroy(h)
+
+
+def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=None, layout=OUT_BFCN, channel_stride=None, out=None):
+    """img [B,C,H,W] (any strides); fix_rc, fix_hw [B,F,2] float32 CUDA.  Returns the sampled
+    tensor in `layout` ([B,F,C,N], [F,B,C,N], [B,F,N,Cp] or [F,B,N,Cp])."""
+    _need_cuda(img, fix_rc, fix_hw)
+    B, Cc, H, W = img.shape
+    fix_rc = fix_rc.to(torch.float32).contiguous()
+    fix_hw = fix_hw.to(torch.float32).contiguous()
+    F = fix_rc.shape[1]
+    assert fix_rc.shape == (B, F, 2) and fix_hw.shape == (B, F, 2)
+    out_dtype = img.dtype if out_dtype is None else out_dtype
+    nc = layout in (OUT_BFNC, OUT_FBNC)
+    cp = (channel_stride or Cc) if nc else Cc
+    lead = (F, B) if layout in (OUT_FBCN, OUT_FBNC) else (B, F)
+    shape = lead + ((plan.n_points, cp) if nc else (Cc, plan.n_points))
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=img.device)
+    else:
+        assert out.shape == shape and out.dtype == out_dtype and out.is_contiguous()
+    strides = (C.c_int64 * 4)(*img.stride())
+    with torch.cuda.device(img.device):
+        check(lib.fovi_sample_forward(plan._h, _ptr(img), _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc), _ptr(fix_hw), F,
+                                      mode, pad, _ptr(out), _dt(out_dtype), layout, cp, _stream()), "fovi_sample_forward")
+    return out
+
+
+class KnnConvPlan:
+    """Device copy of one layer's compacted neighbour/tap tables (fovi_knnconv_plan)."""
+
+    def __init__(self, knn_idx_pad, tap, n_in, V, c_in, c_out, device=None):
+        idx = np.ascontiguousarray(np.asarray(knn_idx_pad, np.int32))
+        tp = np.ascontiguousarray(np.asarray(tap, np.uint16))
+        K, n_out = idx.shape
+        assert tp.shape == (n_out, K), (tp.shape, idx.shape)
+        self.n_in, self.n_out, self.K, self.V, self.c_in, self.c_out = int(n_in), n_out, K, int(V), int(c_in), int(c_out)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib.fovi_knnconv_plan_create(idx.ctypes.data_as(C.c_void_p), tp.ctypes.data_as(C.c_void_p), self.n_in, n_out, K,
+                                               self.V, self.c_in, self.c_out, C.byref(h)), "fovi_knnconv_plan_create")
+        self._h = h
+        self.cin_packed = lib.fovi_knnconv_cin_packed(h)
+        self.nnz = lib.fovi_knnconv_nnz(h)
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib.fovi_knnconv_plan_destroy(h)
+
+    def flops_per_image(self):
+        """Algorithmic FLOPs of one forward for one image: 2 * c_in * c_out * nnz."""
+        return 2 * self.c_in * self.c_out * self.nnz
+
+    def pack_weights(self, weight, dtype=torch.bfloat16):
+        """weight [c_out, c_in*V] (KNNConvLayer.weight) -> slabs [V, c_out, cin_packed]."""
+        _need_cuda(weight)
+        weight = weight.detach().contiguous()
+        assert weight.shape == (self.c_out, self.c_in * self.V)
+        dst = torch.empty((self.V, self.c_out, self.cin_packed), dtype=dtype, device=weight.device)
+        with torch.cuda.device(weight.device):
+            check(lib.fovi_knnconv_pack_weights(self._h, _ptr(weight), _dt(weight.dtype), _ptr(dst), _dt(dtype), _stream()), "fovi_knnconv_pack_weights")
+        return dst
+
+    def forward(self, x_bnc, wt, bias=None, relu=False, out_dtype=torch.bfloat16, out=None):
+        """Tensor-core path.  x_bnc [B,n_in,cin_packed] bf16 contiguous -> [B,n_out,c_out]."""
+        _need_cuda(x_bnc, wt, bias)
+        B = x_bnc.shape[0]
+        assert x_bnc.dtype == torch.bfloat16 and x_bnc.is_contiguous() and x_bnc.shape[1:] == (self.n_in, self.cin_packed), x_bnc.shape
+        assert wt.dtype == torch.bfloat16 and wt.is_contiguous() and wt.shape == (self.V, self.c_out, self.cin_packed)
+        if bias is not None:
+            bias = bias.detach().to(torch.float32).contiguous()
+        if out is None:
+            out = torch.empty((B, self.n_out, self.c_out), dtype=out_dtype, device=x_bnc.device)
+        with torch.cuda.device(x_bnc.device):
+            check(lib.fovi_knnconv_forward(self._h, _ptr(x_bnc), _ptr(wt), _ptr(bias) if bias is not None else None, _ptr(out),
+                                           _dt(out.dtype), B, int(relu), _stream()), "fovi_knnconv_forward")
+        return out
+
+    def forward_f32(self, x, wt_f32, bias=None, relu=False, x_layout=ACT_BCN, y_layout=ACT_BCN):
+        """Exact float32 path.  x [B,c_in,n_in] (BCN) or [B,n_in,c_in] (BNC)."""
+        _need_cuda(x, wt_f32, bias)
+        x = x.contiguous()
+        B = x.shape[0]
+        assert x.shape[1:] == ((self.c_in, self.n_in) if x_layout == ACT_BCN else (self.n_in, self.c_in)), x.shape
+        assert wt_f32.dtype == torch.float32 and wt_f32.shape == (self.V, self.c_out, self.cin_packed)
+        if bias is not None:
+            bias = bias.detach().to(torch.float32).contiguous()
+        shape = (B, self.c_out, self.n_out) if y_layout == ACT_BCN else (B, self.n_out, self.c_out)
+        out = torch.empty(shape, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib.fovi_knnconv_forward_f32(self._h, _ptr(x), _dt(x.dtype), x_layout, _ptr(wt_f32), _ptr(bias) if bias is not None else None,
+                                               _ptr(out), y_layout, B, int(relu), _stream()), "fovi_knnconv_forward_f32")
+        return out
+
+    def check(self):
+        """Synchronise the current stream and raise if a tensor-core launch gave up on a wait."""
+        with torch.cuda.device(self.device):
+            check(lib.fovi_knnconv_check(self._h, _stream()), "fovi_knnconv_check")
+
+
+def pack_points(x, cp):
+    """x [B,C,N] float32/bf16 -> [B,N,cp] bf16, pad channels zero."""
+    _need_cuda(x)
+    x = x.contiguous()
+    B, Cc, N = x.shape
+    dst = torch.empty((B, N, cp), dtype=torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.fovi_pack_points(_ptr(x), _dt(x.dtype), B, Cc, N, _ptr(dst), cp, _stream()), "fovi_pack_points")
+    return dst
+
+
+def launch_count():
+    return lib.fovi_launch_count()

@@ -1,0 +1,160 @@
+/*
+ * fovi_b200 — C ABI of the B200 (sm_100a) foveated hot path: the sensor's grid sample and
+ * the KNNConv layers that consume it.
+ *
+ * The reference (nblauch/fovi) is pure Python and has no FFI; its extension points for this
+ * path are the Python classes cited at each entry point below.  Every function here is what a
+ * binding for that class calls.  Conventions:
+ *   - all image/activation/weight/output buffers are caller-owned DEVICE pointers;
+ *     tables given to *_plan_create are HOST pointers and are copied;
+ *   - work is enqueued on the caller's stream (a cudaStream_t passed as void*); nothing
+ *     synchronises the device except the *_plan_create functions;
+ *   - every function returns a status (0 = FOVI_OK); nothing throws, traps or aborts;
+ *   - a plan may be used from several host threads on distinct streams
+ *     (fovi_knnconv_forward keeps a small per-plan status word that concurrent calls share).
+ */
+#ifndef FOVI_B200_H
+#define FOVI_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  FOVI_OK = 0,
+  FOVI_ERR_INVALID_ARGUMENT = 1, /* null pointer, bad enum, negative size                      */
+  FOVI_ERR_UNSUPPORTED = 2,      /* shape/dtype/layout combination the kernels do not cover    */
+  FOVI_ERR_TABLE_RANGE = 3,      /* neighbour index outside [0, n_in] or tap outside [0, V)    */
+  FOVI_ERR_CUDA = 4,             /* a CUDA runtime/driver call failed (fovi_last_cuda_error)   */
+  FOVI_ERR_ALIGNMENT = 5,        /* pointer or stride not aligned as documented                */
+  FOVI_ERR_DEVICE_TIMEOUT = 6,   /* a bounded in-kernel wait gave up (reported by *_check)     */
+  FOVI_ERR_NO_DEVICE = 7         /* no sm_100 device is current                                */
+} fovi_status;
+
+typedef enum { FOVI_F32 = 0, FOVI_BF16 = 1 } fovi_dtype;
+typedef enum { FOVI_NEAREST = 0, FOVI_BILINEAR = 1 } fovi_sample_mode;
+typedef enum { FOVI_PAD_ZEROS = 0, FOVI_PAD_BORDER = 1 } fovi_pad_mode;
+
+/* Output layouts of the sampler.  B images, F fixations, C channels, N sensor points.       */
+typedef enum {
+  FOVI_OUT_BFCN = 0, /* [B,F,C,N]  what policies.py:277 stacks                                */
+  FOVI_OUT_FBCN = 1, /* [F,B,C,N]  the '(f b) c n' flattening of fovinet.py:281               */
+  FOVI_OUT_BFNC = 2, /* [B,F,N,Cp] points-major, channels last, Cp = out_channel_stride >= C,
+                        channels C..Cp-1 written as 0: the KNNConv kernels' input layout      */
+  FOVI_OUT_FBNC = 3  /* [F,B,N,Cp]                                                            */
+} fovi_sample_layout;
+
+/* Activation layouts of KNNConv. */
+typedef enum {
+  FOVI_ACT_BCN = 0, /* [B,C,N] points last — the reference's layout (knn.py:538-557)          */
+  FOVI_ACT_BNC = 1  /* [B,N,C] channels last                                                   */
+} fovi_act_layout;
+
+const char* fovi_status_string(int status);
+/* Text of the last CUDA error seen by this library on the calling thread ("" if none). */
+const char* fovi_last_cuda_error(void);
+/* Library version, "major.minor". */
+const char* fovi_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Sensor sampler.
+ * Replaces GridSampler (fovi/sensing/samplers.py:51-130): its constructor's
+ * `sampling_grid` (samplers.py:87) is what the plan is built from, and its forward
+ * (samplers.py:91-112: transform_sampling_grid, coords.py:590-642, then F.grid_sample with
+ * align_corners=False) is fovi_sample_forward — for all F fixations of every image in one
+ * launch instead of the per-fixation Python loop of policies.py:266-277.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct fovi_sampler_plan fovi_sampler_plan;
+
+/* grid_xy: HOST [N,2] float32, the rows of GridSampler.sampling_grid[0,0] — (x, -y) of the
+ * sensor's cartesian coordinates in [-1,1].  The plan keeps a spatially sorted copy on the
+ * current device (points are visited in image-tile order; results are written at their
+ * original index).  Synchronises the device. */
+int fovi_sampler_plan_create(const float* grid_xy, int n_points, fovi_sampler_plan** out);
+void fovi_sampler_plan_destroy(fovi_sampler_plan* plan);
+int fovi_sampler_plan_num_points(const fovi_sampler_plan* plan);
+
+/* img        : [B,C,H,W] elements of `dtype`, element strides img_strides[4] (any NCHW or
+ *              NHWC-strided view; no overlap).
+ * fix_rc     : DEVICE [B,F,2] float32, normalised fixation centre (row, col)
+ *              — RetinalTransform._check_fix_loc, retina.py:211-237.
+ * fix_hw     : DEVICE [B,F,2] float32, fixation size in pixels (height, width)
+ *              — RetinalTransform._check_fixation_size, retina.py:176-209.
+ * out        : `out_dtype` elements in `layout`; out_channel_stride is Cp for the *NC layouts
+ *              (ignored otherwise).
+ * Arithmetic is float32 in the reference's operation order; with float32 in and out the result
+ * equals the reference's CPU result bit for bit. */
+int fovi_sample_forward(const fovi_sampler_plan* plan, const void* img, int dtype, int B, int C, int H, int W,
+                        const int64_t* img_strides, const float* fix_rc, const float* fix_hw, int F, int mode,
+                        int pad, void* out, int out_dtype, int layout, int out_channel_stride, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * KNNConv.
+ * Replaces KNNConvLayer.forward (fovi/arch/knn.py:538-557): zero-pad + gather of the K
+ * neighbours (knn.py:484-503), the one-hot tap reassignment local_rf (knn.py:505-526) and the
+ * shared linear map over Cin*V (knn.py:555), evaluated as
+ *   out[b,n,o] = bias[o] + sum_k sum_c X[b, idx[k,n], c] * W[o, c*V + tap[n,k]]
+ * with pad neighbours (idx == n_in) skipped.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct fovi_knnconv_plan fovi_knnconv_plan;
+
+/* knn_idx_pad : HOST [K,n_out] int32 — KNNConvLayer.knn_indices_pad_token (knn.py:451-453),
+ *               values in [0,n_in], n_in marks a pad neighbour.
+ * tap         : HOST [n_out,K] uint16 — argmax over the last axis of the one-hot
+ *               KNNConvLayer.local_rf [n_out,K,V] (knn.py:599-647).
+ * Validates the ranges (FOVI_ERR_TABLE_RANGE), compacts pad entries away and uploads the
+ * tables to the current device.  Synchronises the device. */
+int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16_t* tap, int n_in, int n_out, int K, int V,
+                             int c_in, int c_out, fovi_knnconv_plan** out);
+void fovi_knnconv_plan_destroy(fovi_knnconv_plan* plan);
+
+/* Channel count of the packed bf16 operands: c_in rounded up to a multiple of 8 (64 when
+ * c_in > 8 is a multiple of 64 already).  Activations handed to the tensor-core path are
+ * [B,n_in,cin_packed] bf16 with channels c_in..cin_packed-1 equal to 0. */
+int fovi_knnconv_cin_packed(const fovi_knnconv_plan* plan);
+/* Number of non-pad (n,k) entries: algorithmic FLOPs per image = 2*c_in*c_out*nnz. */
+int64_t fovi_knnconv_nnz(const fovi_knnconv_plan* plan);
+
+/* Repack KNNConvLayer.weight ([c_out, c_in*V], c-major/v-minor, knn.py:462) into V slabs
+ * [V, c_out, cin_packed] of `dst_dtype` (bf16 for the tensor-core path, f32 for the exact
+ * path), zero-filling the padded channels.  W, dst: device pointers. */
+int fovi_knnconv_pack_weights(const fovi_knnconv_plan* plan, const void* W, int w_dtype, void* dst, int dst_dtype,
+                              void* stream);
+/* Bytes of the packed weight buffer for `dst_dtype`. */
+int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* plan, int dst_dtype);
+
+/* Convert activations [B,C,N] (x_dtype, contiguous) to the packed points-major layout
+ * [B,N,cp] bf16 with zero-filled pad channels (cp >= C, multiple of 8). */
+int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, void* stream);
+
+/* Tensor-core path (tcgen05 MMA, bf16 operands, fp32 accumulation in tensor memory).
+ * X    : [B,n_in,cin_packed] bf16, 16-byte aligned.
+ * Wt   : packed bf16 slabs from fovi_knnconv_pack_weights.
+ * bias : [c_out] float32 or NULL.
+ * Y    : [B,n_out,c_out] of y_dtype (bf16 or f32), 16-byte aligned; c_out % 8 == 0.
+ * relu : apply max(.,0) after the bias.
+ * Requires c_out % 16 == 0.  A bounded in-kernel wait that gives up makes the kernel store a
+ * code readable with fovi_knnconv_check; the launch itself still returns FOVI_OK. */
+int fovi_knnconv_forward(fovi_knnconv_plan* plan, const void* X, const void* Wt, const float* bias, void* Y,
+                         int y_dtype, int B, int relu, void* stream);
+
+/* Exact float32 path (CUDA cores, float32 multiply-adds): the fp32 parity case.
+ * X : [B,c_in,n_in] (FOVI_ACT_BCN) or [B,n_in,c_in] (FOVI_ACT_BNC) of x_dtype; Wt: packed
+ * f32 slabs [V,c_out,cin_packed]; Y: float32 in y_layout. */
+int fovi_knnconv_forward_f32(const fovi_knnconv_plan* plan, const void* X, int x_dtype, int x_layout,
+                             const float* Wt, const float* bias, float* Y, int y_layout, int B, int relu,
+                             void* stream);
+
+/* Synchronises `stream` and returns FOVI_ERR_DEVICE_TIMEOUT if any tensor-core launch on this
+ * plan since the last check gave up on a wait; clears the word. */
+int fovi_knnconv_check(fovi_knnconv_plan* plan, void* stream);
+
+/* Number of kernels this library has launched from the calling process (all entry points). */
+int64_t fovi_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FOVI_B200_H */

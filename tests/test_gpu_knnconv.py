@@ -1,0 +1,164 @@
+"""GPU: KNNConv kernels (exact float32 path and tcgen05 bf16 path), called through the C ABI,
+against the oracle and the golden fixtures recorded from the reference."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import synth_images, kaiming_weight
+from oracle import fovi_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+BF16_TOL = 1e-2      # relative L2 of the bf16 tensor-core path vs the float32 reference
+F32_TOL = 1e-5       # max-abs / max-abs of the float32 path vs the float32 reference
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from fovi_b200 import ops
+    return ops
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def rel_max(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def bf16_round(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(torch.bfloat16).to(torch.float32).numpy()
+
+
+def run_tc(ops, plan, x_bcn, w, bias=None, relu=False, out_dtype=torch.float32):
+    wt = plan.pack_weights(dev(w))
+    xp = ops.pack_points(dev(x_bcn), plan.cin_packed)
+    y = plan.forward(xp, wt, None if bias is None else dev(bias), relu=relu, out_dtype=out_dtype)
+    plan.check()
+    return y.to(torch.float32).permute(0, 2, 1).cpu().numpy()
+
+
+def test_config1_f32_path_matches_reference(ops, golden):
+    g = golden("config1.npz")
+    V = int(g["V"])
+    w = kaiming_weight(np.random.RandomState(1), 64, 3, V)
+    plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), V, 3, 64)
+    assert plan.nnz == int((g["knn_idx_pad"] != int(g["n_in"])).sum())
+    wt = plan.pack_weights(dev(w), dtype=torch.float32)
+    y = plan.forward_f32(dev(g["sampled"]), wt).cpu().numpy()
+    assert y.shape == (8, 64, 3975)
+    assert rel_max(y[0], g["conv_out_b0"]) < F32_TOL
+    np.testing.assert_allclose(y.astype(np.float64).sum((1, 2)), g["conv_out_sum"], rtol=1e-5)
+    np.testing.assert_allclose((y.astype(np.float64) ** 2).sum((1, 2)), g["conv_out_sqsum"], rtol=1e-5)
+    # points-major in/out gives the same numbers
+    y2 = plan.forward_f32(dev(g["sampled"].transpose(0, 2, 1)), wt, x_layout=ops.ACT_BNC, y_layout=ops.ACT_BNC).cpu().numpy()
+    assert np.array_equal(y2.transpose(0, 2, 1), y)
+
+
+def test_config1_tensor_core_path(ops, golden):
+    g = golden("config1.npz")
+    V = int(g["V"])
+    w = kaiming_weight(np.random.RandomState(1), 64, 3, V)
+    plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), V, 3, 64)
+    assert plan.cin_packed == 8
+    y = run_tc(ops, plan, g["sampled"], w)
+    assert rel_l2(y[0], g["conv_out_b0"]) < BF16_TOL
+    # against the oracle on bf16-rounded operands the only difference is fp32 summation order
+    ref = oracle.knnconv_forward_closed_form(bf16_round(g["sampled"][:2]), g["knn_idx_pad"], g["tap"].astype(np.int64), V, bf16_round(w))
+    assert rel_max(y[:2], ref) < 1e-4
+
+
+def test_config3_stack_tensor_core(ops, golden):
+    """AlexNet-shaped stack 3->64->192->384->256->256 with ReLU between layers, bf16 activations."""
+    t, acts = golden("config3_tables.npz"), golden("config3_acts_b2.npz")
+    chans = [3, 64, 192, 384, 256, 256]
+    rs = np.random.RandomState(1)
+    x = synth_images(0, (2, 3, 4010))
+    h = ops.pack_points(dev(x), 8)
+    for i in range(5):
+        V = int(t[f"l{i}_V"])
+        w = kaiming_weight(rs, chans[i + 1], chans[i], V)
+        plan = ops.KnnConvPlan(t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"], int(t[f"l{i}_n_in"]), V, chans[i], chans[i + 1])
+        wt = plan.pack_weights(dev(w))
+        h = plan.forward(h, wt, torch.zeros(chans[i + 1], device="cuda"), relu=i < 4, out_dtype=torch.bfloat16)
+        plan.check()
+        got = h.to(torch.float32).permute(0, 2, 1).cpu().numpy()
+        e = rel_l2(got, acts[f"act{i}"])
+        assert e < BF16_TOL, (i, e)
+
+
+@pytest.mark.parametrize("tag", ["p8", "p4"])
+def test_config4_patch_embed(ops, golden, tag):
+    g = golden(f"config4_patch_embed_{tag}.npz")
+    V = int(g["V"])
+    w = kaiming_weight(np.random.RandomState(1), 384, 3, V)
+    b = (0.1 * np.random.RandomState(2).standard_normal(384)).astype(f32)
+    x = synth_images(0, (2, 3, int(g["n_in"])))
+    plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), V, 3, 384)
+    y = run_tc(ops, plan, x, w, b)
+    assert rel_l2(y, g["out_b2"]) < BF16_TOL
+    wt = plan.pack_weights(dev(w), dtype=torch.float32)
+    y32 = plan.forward_f32(dev(x), wt, dev(b)).cpu().numpy()
+    assert rel_max(y32, g["out_b2"]) < F32_TOL
+
+
+@pytest.mark.parametrize("B,Cin,Nin,Nout,K,V,Cout", [
+    (1, 3, 40, 17, 5, 9, 16),        # one image, tiny tables, smallest c_out tile
+    (130, 8, 33, 9, 4, 4, 32),       # batch spills into a second, ragged batch tile
+    (5, 64, 50, 21, 9, 36, 64),      # 64-channel swizzled operand path
+    (3, 128, 30, 11, 7, 16, 384),    # two channel chunks, two c_out tiles of 192
+    (2, 24, 30, 11, 7, 3, 48),       # 24 channels: three 8-channel boxes per neighbour, colliding taps (V < K)
+    (257, 192, 12, 5, 3, 5, 256),    # three batch tiles, widest accumulator
+])
+def test_random_small_cases_vs_oracle(ops, B, Cin, Nin, Nout, K, V, Cout):
+    rs = np.random.RandomState(B * 1000 + Cin)
+    x = rs.standard_normal((B, Cin, Nin)).astype(f32)
+    idx = rs.randint(0, Nin + 1, (K, Nout)).astype(np.int32)      # includes pad token Nin
+    idx[:, 0] = Nin                                                # a point with no neighbours at all
+    tap = rs.randint(0, V, (Nout, K)).astype(np.uint16)
+    w = (rs.standard_normal((Cout, Cin * V)) / np.sqrt(Cin * K)).astype(f32)
+    b = rs.standard_normal(Cout).astype(f32)
+    plan = ops.KnnConvPlan(idx, tap, Nin, V, Cin, Cout)
+    ref = oracle.knnconv_forward_closed_form(bf16_round(x), idx, tap.astype(np.int64), V, bf16_round(w), b, relu=True)
+    y = run_tc(ops, plan, x, w, b, relu=True)
+    assert np.abs(y - ref).max() < 2e-3 * max(1.0, np.abs(ref).max()), np.abs(y - ref).max()
+    np.testing.assert_allclose(y[:, :, 0], np.broadcast_to(np.maximum(b, 0), (B, Cout)), rtol=1e-6, atol=1e-6)
+    ref32 = oracle.knnconv_forward_closed_form(x, idx, tap.astype(np.int64), V, w, b, relu=True)
+    wt32 = plan.pack_weights(dev(w), dtype=torch.float32)
+    y32 = plan.forward_f32(dev(x), wt32, dev(b), relu=True).cpu().numpy()
+    assert rel_max(y32, ref32) < F32_TOL
+    # bf16 output of the tensor-core path
+    y16 = run_tc(ops, plan, x, w, b, relu=True, out_dtype=torch.bfloat16)
+    assert np.abs(y16 - ref).max() < 1e-2 * max(1.0, np.abs(ref).max())
+
+
+def test_linearity_and_determinism_full_batch(ops, golden):
+    """Size-independent properties at a full batch tile count: f(x1 + x2) == f(x1) + f(x2) without
+    bias, and two runs give the same bits."""
+    t = golden("config3_tables.npz")
+    V = int(t["l2_V"])
+    w = kaiming_weight(np.random.RandomState(3), 384, 192, V)
+    plan = ops.KnnConvPlan(t["l2_knn_idx_pad"], t["l2_tap"], 225, V, 192, 384)
+    wt = plan.pack_weights(dev(w))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    # integers/8 are exact in bf16 and so are their pairwise sums
+    x1 = (torch.randint(-8, 9, (256, 225, 192), device="cuda", generator=g) / 8).to(torch.bfloat16)
+    x2 = (torch.randint(-8, 9, (256, 225, 192), device="cuda", generator=g) / 8).to(torch.bfloat16)
+    y1 = plan.forward(x1, wt, out_dtype=torch.float32); y2 = plan.forward(x2, wt, out_dtype=torch.float32)
+    y12 = plan.forward(x1 + x2, wt, out_dtype=torch.float32); y12b = plan.forward(x1 + x2, wt, out_dtype=torch.float32)
+    plan.check()
+    assert torch.equal(y12, y12b)
+    assert float((y12 - (y1 + y2)).abs().max()) < 1e-3 * float(y12.abs().max())
+
+
+def test_empty_batch(ops, golden):
+    g = golden("config4_patch_embed_p8.npz")
+    plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), int(g["V"]), 3, 384)
+    wt = torch.zeros((int(g["V"]), 384, 8), dtype=torch.bfloat16, device="cuda")
+    y = plan.forward(torch.empty((0, int(g["n_in"]), 8), dtype=torch.bfloat16, device="cuda"), wt)
+    assert y.shape == (0, plan.n_out, 384)

@@ -1,0 +1,102 @@
+"""CPU: the NumPy oracle reproduces the outputs recorded from the reference (tests/golden)."""
+import numpy as np
+import pytest
+
+from conftest import synth_images, kaiming_weight
+from oracle import fovi_oracle as oracle
+
+f32 = np.float32
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
+
+def test_config1_sampler_bit_exact(golden):
+    g, s = golden("config1.npz"), golden("sensor_a2p78.npz")
+    x = synth_images(0, (8, 3, 224, 224))
+    y = oracle.retinal_sample(x, s["sampling_grid"], None, np.full((8, 2), 224, f32))
+    assert y.shape == (8, 3, 3975)
+    assert np.array_equal(y, g["sampled"])
+
+
+def test_config1_knnconv(golden):
+    g = golden("config1.npz")
+    w = kaiming_weight(np.random.RandomState(1), 64, 3, 49)
+    out = oracle.knnconv_forward(g["sampled"], g["knn_idx_pad"], g["tap"].astype(np.int64), int(g["V"]), w)
+    assert rel_err(out[0], g["conv_out_b0"]) < 1e-5
+    np.testing.assert_allclose(out.astype(np.float64).sum((1, 2)), g["conv_out_sum"], rtol=1e-6)
+    np.testing.assert_allclose((out.astype(np.float64) ** 2).sum((1, 2)), g["conv_out_sqsum"], rtol=1e-6)
+    out2 = oracle.knnconv_forward_closed_form(g["sampled"][:2], g["knn_idx_pad"], g["tap"].astype(np.int64), int(g["V"]), w)
+    assert rel_err(out2[0], g["conv_out_b0"]) < 1e-5
+
+
+@pytest.mark.parametrize("tag", ["a1", "a2p78", "a60p94"])
+@pytest.mark.parametrize("mode", ["bilinear", "nearest"])
+def test_config2_sampler_modes_bit_exact(golden, tag, mode):
+    g, s = golden("config2_small.npz"), golden(f"sensor_{tag}.npz")
+    x = synth_images(0, (2, 3, 256, 256))
+    fs = float(g[f"{tag}_default_size"])
+    full = np.full((2, 3, 2), fs, f32)
+    grid = s["sampling_grid"]
+    assert np.array_equal(oracle.retinal_sample(x, grid, g["fix"], full, mode, "zeros"), g[f"{tag}_{mode}_near_zeros"])
+    assert np.array_equal(oracle.retinal_sample(x, grid, g["fix"], g["sizes"], mode, "zeros"), g[f"{tag}_{mode}_near_sizes"])
+    assert np.array_equal(oracle.retinal_sample(x, grid, g["fix_any"], full, mode, "zeros"), g[f"{tag}_{mode}_any_zeros"])
+    assert np.array_equal(oracle.retinal_sample(x, grid, g["fix_any"], full, mode, "border"), g[f"{tag}_{mode}_any_border"])
+
+
+def test_known_point_counts(golden):
+    """Point counts printed by the reference's notebooks (step2_knnconv cells 10-18, step4 cell 9)."""
+    assert golden("sensor_a0p5.npz")["cartesian"].shape[0] == 4085
+    assert int(golden("sensor_a0p5.npz")["resolution"]) == 53
+    assert int(golden("pool_a0p5.npz")["n_out"]) == 964
+    assert golden("sensor_a2p785765.npz")["cartesian"].shape[0] == 3976
+    t = golden("config3_tables.npz")
+    assert [int(t[f"l{i}_n_in"]) for i in range(5)] == [4010, 1023, 225, 225, 225]
+    assert [int(t[f"l{i}_V"]) for i in range(5)] == [484, 100, 36, 36, 36]
+
+
+def test_config3_stack(golden):
+    t, acts = golden("config3_tables.npz"), golden("config3_acts_b2.npz")
+    chans = [3, 64, 192, 384, 256, 256]
+    rs = np.random.RandomState(1)
+    h = synth_images(0, (2, 3, 4010))
+    for i in range(5):
+        V = int(t[f"l{i}_V"])
+        w = kaiming_weight(rs, chans[i + 1], chans[i], V)
+        h = oracle.knnconv_forward(h, t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"].astype(np.int64), V, w, np.zeros(chans[i + 1], f32))
+        if i < 4:
+            h = np.maximum(h, 0)
+        assert rel_err(h, acts[f"act{i}"]) < 1e-5, i
+
+
+@pytest.mark.parametrize("tag", ["p8", "p4"])
+def test_config4_patch_embed(golden, tag):
+    g = golden(f"config4_patch_embed_{tag}.npz")
+    V = int(g["V"])
+    w = kaiming_weight(np.random.RandomState(1), 384, 3, V)
+    b = (0.1 * np.random.RandomState(2).standard_normal(384)).astype(f32)
+    x = synth_images(0, (2, 3, int(g["n_in"])))
+    out = oracle.knnconv_forward(x, g["knn_idx_pad"], g["tap"].astype(np.int64), V, w, b)
+    assert rel_err(out, g["out_b2"]) < 1e-5
+
+
+def test_pool_max(golden):
+    g = golden("pool_a0p5.npz")
+    x = synth_images(5, (2, 4, int(g["n_in"]))) - f32(0.5)
+    assert np.array_equal(oracle.knn_pool_max(x, g["knn_idx_pad"]), g["out"])
+
+
+def test_closed_form_handles_pad_and_collisions():
+    rs = np.random.RandomState(7)
+    B, Cin, Nin, Nout, K, V, Cout = 3, 5, 11, 7, 6, 4, 8   # V < K forces colliding taps
+    x = rs.standard_normal((B, Cin, Nin)).astype(f32)
+    idx = rs.randint(0, Nin + 1, (K, Nout))               # includes pad token Nin
+    idx[:, 0] = Nin                                        # a point whose neighbours are all pads
+    tap = rs.randint(0, V, (Nout, K))
+    w = rs.standard_normal((Cout, Cin * V)).astype(f32)
+    b = rs.standard_normal(Cout).astype(f32)
+    a = oracle.knnconv_forward(x, idx, tap, V, w, b)
+    c = oracle.knnconv_forward_closed_form(x, idx, tap, V, w, b)
+    np.testing.assert_allclose(a, c, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(a[:, :, 0], np.broadcast_to(b, (B, Cout)), rtol=1e-6)
