@@ -147,8 +147,9 @@ extern "C" int fovi_knnconv_pack_weights(const fovi_knnconv_plan* p, const void*
 }
 
 extern "C" int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, void* stream) {
-  if (!x || !dst || !fovi::valid_dtype(x_dtype) || B < 0 || C <= 0 || N <= 0 || cp < C || cp % 8) return FOVI_ERR_INVALID_ARGUMENT;
+  if (!fovi::valid_dtype(x_dtype) || B < 0 || C <= 0 || N <= 0 || cp < C || cp % 8) return FOVI_ERR_INVALID_ARGUMENT;
   if (B == 0) return FOVI_OK;
+  if (!x || !dst) return FOVI_ERR_INVALID_ARGUMENT;
   if (B > 65535) return FOVI_ERR_UNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid((N + 31) / 32, (cp + 31) / 32, B), block(32, 8);
@@ -159,7 +160,8 @@ extern "C" int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N,
 
 extern "C" int fovi_knnconv_forward_f32(const fovi_knnconv_plan* p, const void* X, int x_dtype, int x_layout, const float* Wt,
                                         const float* bias, float* Y, int y_layout, int B, int relu, void* stream) {
-  if (!p || !X || !Wt || !Y || !fovi::valid_dtype(x_dtype) || B < 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if (!p || !fovi::valid_dtype(x_dtype) || B < 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B > 0 && (!X || !Wt || !Y)) return FOVI_ERR_INVALID_ARGUMENT;
   if ((x_layout != FOVI_ACT_BCN && x_layout != FOVI_ACT_BNC) || (y_layout != FOVI_ACT_BCN && y_layout != FOVI_ACT_BNC))
     return FOVI_ERR_INVALID_ARGUMENT;
   if (B == 0) return FOVI_OK;

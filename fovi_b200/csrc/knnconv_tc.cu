@@ -277,7 +277,9 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const int t = item / a.n_ct;
       const int n = t % a.n_out, mt = t / a.n_out;
       const int cnt = __ldg(a.nbr_cnt + n);
-      if (!mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4)) { ok = false; break; }
+      ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4);
+      ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave as a whole warp or not at all
+      if (!ok) break;
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
       const int o0 = ctile * a.ct;
@@ -376,8 +378,9 @@ int pick_cout_tile(int c_out) {
 
 extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
                                     int y_dtype, int B, int relu, void* stream) {
-  if (!p || !X || !Wt || !Y || B < 0 || !fovi::valid_dtype(y_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
-  if (B == 0) return FOVI_OK;
+  if (!p || B < 0 || !fovi::valid_dtype(y_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;  // an empty batch has no buffers to look at
+  if (!X || !Wt || !Y) return FOVI_ERR_INVALID_ARGUMENT;
   if (p->c_out % 16) return FOVI_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Wt) | reinterpret_cast<uintptr_t>(Y)) & 15) return FOVI_ERR_ALIGNMENT;
   const int ct = pick_cout_tile(p->c_out);

@@ -225,7 +225,8 @@ extern "C" int fovi_sampler_plan_num_points(const fovi_sampler_plan* plan) { ret
 extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* img, int dtype, int B, int C, int H, int W,
                                    const int64_t* img_strides, const float* fix_rc, const float* fix_hw, int F, int mode,
                                    int pad, void* out, int out_dtype, int layout, int out_channel_stride, void* stream) {
-  if (!plan || !img || !img_strides || !fix_rc || !fix_hw || !out) return FOVI_ERR_INVALID_ARGUMENT;
+  if (!plan || !img_strides) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B > 0 && (!img || !fix_rc || !fix_hw || !out)) return FOVI_ERR_INVALID_ARGUMENT;
   if (B < 0 || C <= 0 || H <= 0 || W <= 0 || F <= 0) return FOVI_ERR_INVALID_ARGUMENT;
   if (!fovi::valid_dtype(dtype) || !fovi::valid_dtype(out_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   if (mode != FOVI_NEAREST && mode != FOVI_BILINEAR) return FOVI_ERR_INVALID_ARGUMENT;
