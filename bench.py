@@ -1,0 +1,278 @@
+#!/usr/bin/env python
+"""Benchmark of the foveated hot path on B200: sensor sampling of F fixations per image followed by
+the fovi-AlexNet-shaped KNNConv stack.  Prints ONE JSON line (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step = one pass of the hot path over one batch: `--batch` images of 3x256x256 (float32, uniform
+[0,1), synthetic) x `--fixations` fixations -> sensor (a=1, ~4010 points, bilinear, zeros padding)
+-> KNNConv 3->64->192->384->256->256 with ReLU between layers (bf16 operands, fp32 accumulation).
+`value` is image x fixations per second with the images resident in HBM; `e2e` is the same metric
+through the public module API with pinned HOST images in and the final activations copied back to the
+host inside the timed region.  With N > 1 every rank runs its own batch (weak scaling, no collective
+on the path); times are the max over ranks.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CHANS = [3, 64, 192, 384, 256, 256]
+METRIC = "images x fixations/s through sensor+KNNConv"
+UNIT = "img*fix/s"
+
+
+def load_tables():
+    t = dict(np.load(os.path.join(ROOT, "tests", "golden", "config3_tables.npz")))
+    s = dict(np.load(os.path.join(ROOT, "tests", "golden", "sensor_a1.npz")))
+    return s, t
+
+
+def make_weights():
+    rs = np.random.RandomState(1)
+    s, t = load_tables()
+    ws = []
+    for i in range(5):
+        V = int(t[f"l{i}_V"])
+        ws.append((rs.standard_normal((CHANS[i + 1], CHANS[i] * V)) * np.sqrt(2.0 / (CHANS[i] * V))).astype(np.float32))
+    return ws
+
+
+def workload_name(args):
+    return (f"sensor(a=1,N=4010,bilinear,zeros) x {args.fixations} fixations on {args.batch}x3x256x256 fp32 images "
+            f"+ KNNConv stack 3-64-192-384-256-256 (K=121,25,9,9,9; bf16, fp32 accumulate)")
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons in the background during the timed region."""
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 7 for i in range(4) if r[3 + i].lower().startswith("active")})
+        pw = [float(r[2]) for r in self.rows if len(r) >= 7 and r[2].replace(".", "").isdigit()]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": reasons}
+
+
+def cpu_baseline(n_images, n_fix, threads):
+    """The oracle (a NumPy port of the reference's CPU path) timed on a bounded sample of the workload."""
+    from oracle import fovi_oracle as oracle
+    s, t = load_tables()
+    ws = make_weights()
+    rs = np.random.RandomState(0)
+    x = rs.random_sample((n_images, 3, 256, 256)).astype(np.float32)
+    fix = (0.25 + 0.5 * rs.random_sample((n_images, n_fix, 2))).astype(np.float32)
+    hw = np.full((n_images, n_fix, 2), 256, np.float32)
+
+    def run():
+        y = oracle.retinal_sample(x, s["sampling_grid"], fix, hw)                       # [B,F,3,N]
+        h = y.transpose(1, 0, 2, 3).reshape(n_images * n_fix, 3, -1)                     # (f b) c n
+        for i in range(5):
+            h = oracle.knnconv_forward(h, t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"].astype(np.int64), int(t[f"l{i}_V"]), ws[i], np.zeros(CHANS[i + 1], np.float32))
+            if i < 4:
+                h = np.maximum(h, 0)
+        return h
+    run()
+    t0 = time.perf_counter(); reps = 0
+    while reps < 2 or time.perf_counter() - t0 < 8.0:
+        run(); reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return n_images * n_fix / dt, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count()
+    n_img, n_fix = 2, args.fixations
+    vals = []
+    for _ in range(args.warmup):
+        cpu_baseline(n_img, n_fix, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        v, dt = cpu_baseline(n_img, n_fix, threads)
+        vals.append(v)
+    v = float(np.median(vals))
+    sample = f"{n_img} images x {n_fix} fixations per step (same sensor, tables and weights), float32"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * n_img * n_fix / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": workload_name(args), "sample": sample},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
+    ap.add_argument("--fixations", type=int, default=4)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from fovi_b200 import ops
+
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+
+    s, t = load_tables()
+    ws = make_weights()
+    B, F = args.batch, args.fixations
+    M = B * F
+    splan = ops.SamplerPlan(s["sampling_grid"], dev)
+    plans, wts, biases = [], [], []
+    for i in range(5):
+        p = ops.KnnConvPlan(t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"], int(t[f"l{i}_n_in"]), int(t[f"l{i}_V"]), CHANS[i], CHANS[i + 1], dev)
+        plans.append(p); wts.append(p.pack_weights(torch.from_numpy(ws[i]).to(dev))); biases.append(torch.zeros(CHANS[i + 1], device=dev))
+    rs = np.random.RandomState(1000 + rank)
+    x_host = torch.from_numpy(rs.random_sample((B, 3, 256, 256)).astype(np.float32)).pin_memory()
+    fix_host = torch.from_numpy((0.25 + 0.5 * rs.random_sample((B, F, 2))).astype(np.float32)).pin_memory()
+    hw = torch.full((B, F, 2), 256.0, device=dev)
+    x_dev = x_host.to(dev); fix_dev = fix_host.to(dev)
+    # preallocated activations (channels-last points layout), reused every step
+    acts = [torch.empty(((splan.n_points + 1) // 2, M, 8), dtype=torch.bfloat16, device=dev)]   # pair layout
+    for i in range(5):
+        acts.append(torch.empty((M, plans[i].n_out, CHANS[i + 1]), dtype=torch.bfloat16, device=dev))
+    out_host = torch.empty(acts[-1].shape, dtype=torch.bfloat16).pin_memory()
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+    kernel_events = []
+
+    def step(x, fix, record=None):
+        marks = [ev() for _ in range(7)] if record is not None else None
+        if marks: marks[0].record()
+        ops.sample(splan, x, fix, hw, layout=ops.OUT_FB_PAIRS, out=acts[0])
+        if marks: marks[1].record()
+        for i in range(5):
+            plans[i].forward(acts[i], wts[i], biases[i], relu=i < 4, out=acts[i + 1])
+            if marks: marks[i + 2].record()
+        if marks: record.append(marks)
+        return acts[-1]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, record=None):
+        for _ in range(warmup):
+            flush.zero_(); fn(None)
+        barrier()
+        t = 0.0
+        l0 = ops.launch_count()
+        for _ in range(steps):
+            flush.zero_()                       # L2 flush between timed iterations (excluded from the time)
+            a, b = ev(), ev()
+            a.record(); fn(record); b.record()
+            b.synchronize()
+            t += a.elapsed_time(b)
+        barrier()
+        tt = torch.tensor([t], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item()), ops.launch_count() - l0
+
+    clocks = ClockSampler(local)
+    clocks.start()
+    ms_total, launches = timed(lambda rec: step(x_dev, fix_dev, rec), args.steps, max(args.warmup, 3), kernel_events)
+
+    def e2e_step(_):
+        xd = x_host.to(dev, non_blocking=True); fd = fix_host.to(dev, non_blocking=True)
+        y = step(xd, fd)
+        out_host.copy_(y, non_blocking=True)
+    ms_e2e, _ = timed(e2e_step, args.steps, 3)
+    clk = clocks.stop()
+    for p in plans:
+        p.check()
+
+    # per-kernel times from the events recorded inside the timed steps
+    per = np.zeros(6)
+    for marks in kernel_events:
+        for i in range(6):
+            per[i] += marks[i].elapsed_time(marks[i + 1])
+    per /= max(len(kernel_events), 1)                      # ms per launch: [sampler, conv0..conv4]
+    flops = [M * p.flops_per_image() for p in plans]
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        d = json.load(open(pk)); peaks = {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops_sustained"], "src": "measured (sustained)"}
+    conv_ms = per[1:].sum()
+    conv_tflops = sum(flops) / (conv_ms * 1e-3) / 1e12
+    layers = [{"layer": i, "ms": float(per[i + 1]), "tflops": flops[i] / (per[i + 1] * 1e-3) / 1e12} for i in range(5)]
+
+    if rank == 0:
+        from oracle import fovi_oracle as oracle
+        fx = fix_host.numpy().reshape(-1, 2)[: 64]
+        samp_bytes, mean_u = oracle.sampler_footprint_bytes(s["sampling_grid"], fx, np.full_like(fx, 256), 256, 256, 3, 4, 2)
+        samp_bytes_per = samp_bytes / fx.shape[0]
+        sampler_gbs = samp_bytes_per * M / (per[0] * 1e-3) / 1e9
+        value = world * M * args.steps / (ms_total * 1e-3)
+        e2e = world * M * args.steps / (ms_e2e * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": {"workload": workload_name(args), "images_per_gpu": B, "fixations": F, "l2": "flushed between steps (192 MB write)"},
+            "roofline": {"bound": "tensor", "kernel": "fovi_knnconv_tc_kernel (5 launches per step)", "achieved": conv_tflops, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": conv_tflops / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["src"],
+                         "flops_per_launch_avg": sum(flops) / 5, "ms_per_launch_avg": conv_ms / 5},
+            "layers": layers,
+            "sampler": {"ms": float(per[0]), "algorithmic_bytes_per_imgfix": samp_bytes_per, "mean_unique_pixels": mean_u, "gbs": sampler_gbs,
+                        "frac_of_hbm": sampler_gbs / peaks["hbm_gbs"]},
+            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 4 + fix_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 2,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(launches), "clocks": clk,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, dt = cpu_baseline(2, F, os.cpu_count())
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                                    "sample": f"2 images x {F} fixations per pass, float32 NumPy port of the reference path"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

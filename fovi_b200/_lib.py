@@ -24,9 +24,10 @@ SIGNATURES = {
     "fovi_knnconv_plan_destroy": (None, [_P]),
     "fovi_knnconv_cin_packed": (C.c_int, [_P]),
     "fovi_knnconv_nnz": (C.c_int64, [_P]),
+    "fovi_knnconv_x_layout": (C.c_int, [_P]),
     "fovi_knnconv_pack_weights": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, _P]),
     "fovi_knnconv_packed_weight_bytes": (C.c_int64, [_P, C.c_int]),
-    "fovi_pack_points": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_int, _P]),
+    "fovi_pack_points": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_forward": (C.c_int, [_P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knnconv_forward_f32": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knnconv_check": (C.c_int, [_P, _P]),

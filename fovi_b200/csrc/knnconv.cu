@@ -1,4 +1,5 @@
 // KNNConv: plan construction, operand packing and the exact float32 (CUDA-core) forward.
+#include <algorithm>
 #include <vector>
 
 #include "knnconv_plan.cuh"
@@ -15,6 +16,42 @@ __global__ void pack_weights_kernel(const TW* __restrict__ W, TD* __restrict__ d
     const int v = (int)(i / ((long long)cp * c_out));
     const float w = c < c_in ? ld_as_float(W + ((long long)o * c_in + c) * V + v) : 0.f;
     dst[i] = from_float<TD>(w);
+  }
+}
+
+// Pair mode: W [c_out, c_in*V] -> per-output-point slabs [n_out, sp, c_out, 8]; element (h, c) of a
+// slot row is the weight of channel c (< 4) for the even (h = 0) or odd (h = 1) point of the pair.
+template <typename TW>
+__global__ void pack_weights_pairs_kernel(const TW* __restrict__ W, __nv_bfloat16* __restrict__ dst,
+                                          const uint16_t* __restrict__ pair_tap, int n_out, int sp, int V, int c_out, int c_in) {
+  const long long total = (long long)n_out * sp * c_out * 8;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int e = (int)(i & 7);
+    const int o = (int)((i >> 3) % c_out);
+    const long long slot = (i >> 3) / c_out;  // n*sp + s
+    const int h = e >> 2, c = e & 3;
+    const int t = pair_tap[slot * 2 + h];
+    const float w = (c < c_in && t != 0xFFFF) ? ld_as_float(W + ((long long)o * c_in + c) * V + t) : 0.f;
+    dst[i] = __float2bfloat16_rn(w);
+  }
+}
+
+// X [B,C,N] -> [ceil(N/2), B, 2, 4] bf16 (pair layout), one thread per (pair, image).
+template <typename TX>
+__global__ void pack_points_pairs_kernel(const TX* __restrict__ x, __nv_bfloat16* __restrict__ dst, int B, int C, int N) {
+  const int n_pairs = (N + 1) / 2;
+  const long long total = (long long)n_pairs * B;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int pr = (int)(i % n_pairs), b = (int)(i / n_pairs);
+    __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int n = 2 * pr + h;
+        v[h * 4 + c] = __float2bfloat16_rn((c < C && n < N) ? ld_as_float(x + ((long long)b * C + c) * N + n) : 0.f);
+      }
+    *reinterpret_cast<uint4*>(dst + ((long long)pr * B + b) * 8) = *reinterpret_cast<const uint4*>(v);
   }
 }
 
@@ -96,7 +133,56 @@ extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16
   auto* p = new fovi_knnconv_plan();
   p->n_in = n_in; p->n_out = n_out; p->K = K; p->V = V; p->c_in = c_in; p->c_out = c_out; p->kp = kp; p->nnz = nnz;
   p->cin_packed = (c_in % 64 == 0) ? c_in : (c_in + 7) / 8 * 8;
+  // Pair mode for tiny channel counts: group each point's neighbours into aligned input pairs
+  // (2p, 2p+1).  A neighbour takes the free half of a slot of its pair, or opens a new slot (so a
+  // table that lists the same input point twice still adds both taps).
+  std::vector<int> pidx, pcnt;
+  std::vector<uint16_t> ptap;
+  if (c_in <= 4) {
+    p->x_layout = FOVI_X_PAIRS;
+    p->n_pairs = (n_in + 1) / 2;
+    std::vector<std::vector<int>> slots_idx(n_out);
+    std::vector<std::vector<uint16_t>> slots_tap(n_out);
+    int max_slots = 0;
+    for (int n = 0; n < n_out; ++n) {
+      auto& si = slots_idx[n];
+      auto& st = slots_tap[n];
+      for (int m = 0; m < cnt[n]; ++m) {
+        const int j = idx[(size_t)n * kp + m], pr = j >> 1, h = j & 1;
+        size_t s = 0;
+        for (; s < si.size(); ++s)
+          if (si[s] == pr && st[2 * s + h] == 0xFFFF) break;
+        if (s == si.size()) { si.push_back(pr); st.push_back(0xFFFF); st.push_back(0xFFFF); }
+        st[2 * s + h] = tp[(size_t)n * kp + m];
+      }
+      max_slots = std::max<int>(max_slots, (int)si.size());
+    }
+    p->sp = std::max(8, (max_slots + 7) / 8 * 8);
+    pidx.assign((size_t)n_out * p->sp, p->n_pairs);
+    ptap.assign((size_t)n_out * p->sp * 2, 0xFFFF);
+    pcnt.assign(n_out, 0);
+    for (int n = 0; n < n_out; ++n) {
+      // visit pairs in ascending order: neighbouring slots then read neighbouring memory
+      std::vector<int> order(slots_idx[n].size());
+      for (size_t s = 0; s < order.size(); ++s) order[s] = (int)s;
+      std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return slots_idx[n][a] < slots_idx[n][b]; });
+      for (size_t s = 0; s < order.size(); ++s) {
+        pidx[(size_t)n * p->sp + s] = slots_idx[n][order[s]];
+        ptap[((size_t)n * p->sp + s) * 2] = slots_tap[n][2 * order[s]];
+        ptap[((size_t)n * p->sp + s) * 2 + 1] = slots_tap[n][2 * order[s] + 1];
+      }
+      pcnt[n] = (int)order.size();
+    }
+  }
   cudaError_t e = cudaGetDevice(&p->device);
+  if (e == cudaSuccess && p->x_layout == FOVI_X_PAIRS) {
+    e = cudaMalloc(&p->pair_idx, sizeof(int) * pidx.size());
+    if (e == cudaSuccess) e = cudaMalloc(&p->pair_cnt, sizeof(int) * n_out);
+    if (e == cudaSuccess) e = cudaMalloc(&p->pair_tap, sizeof(uint16_t) * ptap.size());
+    if (e == cudaSuccess) e = cudaMemcpy(p->pair_idx, pidx.data(), sizeof(int) * pidx.size(), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(p->pair_cnt, pcnt.data(), sizeof(int) * n_out, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(p->pair_tap, ptap.data(), sizeof(uint16_t) * ptap.size(), cudaMemcpyHostToDevice);
+  }
   if (e == cudaSuccess) e = cudaMalloc(&p->nbr_idx, sizeof(int) * idx.size());
   if (e == cudaSuccess) e = cudaMalloc(&p->nbr_tap, sizeof(uint16_t) * tp.size());
   if (e == cudaSuccess) e = cudaMalloc(&p->nbr_cnt, sizeof(int) * n_out);
@@ -119,14 +205,19 @@ extern "C" void fovi_knnconv_plan_destroy(fovi_knnconv_plan* p) {
   if (p->nbr_tap) cudaFree(p->nbr_tap);
   if (p->nbr_cnt) cudaFree(p->nbr_cnt);
   if (p->status) cudaFree(p->status);
+  if (p->pair_idx) cudaFree(p->pair_idx);
+  if (p->pair_cnt) cudaFree(p->pair_cnt);
+  if (p->pair_tap) cudaFree(p->pair_tap);
   delete p;
 }
 
 extern "C" int fovi_knnconv_cin_packed(const fovi_knnconv_plan* p) { return p ? p->cin_packed : -1; }
 extern "C" int64_t fovi_knnconv_nnz(const fovi_knnconv_plan* p) { return p ? p->nnz : -1; }
+extern "C" int fovi_knnconv_x_layout(const fovi_knnconv_plan* p) { return p ? p->x_layout : -1; }
 
 extern "C" int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* p, int dst_dtype) {
   if (!p || !fovi::valid_dtype(dst_dtype)) return -1;
+  if (p->x_layout == FOVI_X_PAIRS && dst_dtype == FOVI_BF16) return (int64_t)p->n_out * p->sp * p->c_out * 8 * 2;
   return (int64_t)p->V * p->c_out * p->cin_packed * (int64_t)fovi::dtype_size(dst_dtype);
 }
 
@@ -134,6 +225,15 @@ extern "C" int fovi_knnconv_pack_weights(const fovi_knnconv_plan* p, const void*
                                          void* stream) {
   if (!p || !W || !dst || !fovi::valid_dtype(w_dtype) || !fovi::valid_dtype(dst_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (p->x_layout == FOVI_X_PAIRS && dst_dtype == FOVI_BF16) {
+    const long long tot = (long long)p->n_out * p->sp * p->c_out * 8;
+    const int g = (int)std::min<long long>((tot + 255) / 256, 148 * 32);
+    if (w_dtype == FOVI_F32)
+      pack_weights_pairs_kernel<float><<<g, 256, 0, st>>>((const float*)W, (__nv_bfloat16*)dst, p->pair_tap, p->n_out, p->sp, p->V, p->c_out, p->c_in);
+    else
+      pack_weights_pairs_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)W, (__nv_bfloat16*)dst, p->pair_tap, p->n_out, p->sp, p->V, p->c_out, p->c_in);
+    return fovi::after_launch("pack_weights_pairs_kernel");
+  }
   const long long total = (long long)p->V * p->c_out * p->cin_packed;
   const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
 #define PACK(TW, TD) \
@@ -146,12 +246,22 @@ extern "C" int fovi_knnconv_pack_weights(const fovi_knnconv_plan* p, const void*
   return fovi::after_launch("pack_weights_kernel");
 }
 
-extern "C" int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, void* stream) {
-  if (!fovi::valid_dtype(x_dtype) || B < 0 || C <= 0 || N <= 0 || cp < C || cp % 8) return FOVI_ERR_INVALID_ARGUMENT;
+extern "C" int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, int x_layout, void* stream) {
+  if (!fovi::valid_dtype(x_dtype) || B < 0 || C <= 0 || N <= 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if (x_layout != FOVI_X_BNC && x_layout != FOVI_X_PAIRS) return FOVI_ERR_INVALID_ARGUMENT;
+  if (x_layout == FOVI_X_BNC && (cp < C || cp % 8)) return FOVI_ERR_INVALID_ARGUMENT;
+  if (x_layout == FOVI_X_PAIRS && C > 4) return FOVI_ERR_INVALID_ARGUMENT;
   if (B == 0) return FOVI_OK;
   if (!x || !dst) return FOVI_ERR_INVALID_ARGUMENT;
   if (B > 65535) return FOVI_ERR_UNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (x_layout == FOVI_X_PAIRS) {
+    const long long tot = (long long)((N + 1) / 2) * B;
+    const int g = (int)std::min<long long>((tot + 255) / 256, 148 * 32);
+    if (x_dtype == FOVI_F32) pack_points_pairs_kernel<float><<<g, 256, 0, st>>>((const float*)x, (__nv_bfloat16*)dst, B, C, N);
+    else pack_points_pairs_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)dst, B, C, N);
+    return fovi::after_launch("pack_points_pairs_kernel");
+  }
   dim3 grid((N + 31) / 32, (cp + 31) / 32, B), block(32, 8);
   if (x_dtype == FOVI_F32) pack_points_kernel<float><<<grid, block, 0, st>>>((const float*)x, (__nv_bfloat16*)dst, C, N, cp);
   else pack_points_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)dst, C, N, cp);

@@ -14,4 +14,11 @@ struct fovi_knnconv_plan {
   uint16_t* nbr_tap = nullptr;  // [n_out, kp]
   int* nbr_cnt = nullptr;       // [n_out]
   int* status = nullptr;        // device word written by a tensor-core kernel whose wait gave up
+  // Pair mode (c_in <= 4): neighbours grouped into aligned point pairs (2p, 2p+1).
+  int x_layout = FOVI_X_BNC;
+  int n_pairs = 0;              // ceil(n_in / 2)
+  int sp = 0;                   // pair-slot pitch per output point (multiple of 8)
+  int* pair_idx = nullptr;      // [n_out, sp] pair index; unused slots hold n_pairs (reads as zero)
+  int* pair_cnt = nullptr;      // [n_out]
+  uint16_t* pair_tap = nullptr; // [n_out, sp, 2] tap of the even / odd member, 0xFFFF = not a neighbour
 };

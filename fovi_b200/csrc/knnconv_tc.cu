@@ -18,13 +18,18 @@
 //   warps 2-5   epilogue: tcgen05.ld the finished accumulator (double-buffered in tensor
 //               memory so the next item's MMAs overlap), add bias, ReLU, convert, store.
 //
-// Two operand modes:
-//   C64  channels packed to a multiple of 64: a stage is one 64-channel chunk of one neighbour,
-//        128-byte-swizzled K-major tiles (4 MMAs of K=16 per stage);
-//   C8   any multiple of 8 channels (the 3-channel first layer packs to 8): a stage is eight
-//        (neighbour, 8-channel chunk) boxes of 16-byte rows in the un-swizzled core-matrix
-//        layout; one MMA (K=16) consumes two boxes.  Tail boxes read the out-of-range point
-//        index n_in, which TMA fills with zeros.
+// Three operand modes:
+//   C64    channels packed to a multiple of 64: a stage is one 64-channel chunk of one neighbour,
+//          128-byte-swizzled K-major tiles (4 MMAs of K=16 per stage);
+//   C8     any other multiple of 8 channels: a stage is eight (neighbour, 8-channel chunk) boxes
+//          of 16-byte rows in the un-swizzled core-matrix layout; one MMA (K=16) consumes two
+//          boxes.  Tail boxes read the out-of-range point index n_in, which TMA fills with zeros;
+//   PAIRS  c_in <= 4 (RGB first layers, patch embeddings): activations are stored pair-major,
+//          [point pair][batch row][2 points x 4 channels], so the 128 batch rows of one pair are
+//          ONE contiguous 2 KB block (a 16-byte-row box like C8, but 16x fewer memory rows than
+//          gathering 128 strided rows), and the weights are pre-gathered per output point so the
+//          eight slabs of a stage are one contiguous box.  One MMA (K=16) consumes two pairs =
+//          four neighbours.
 //
 // Every wait is bounded: a wait that gives up raises a CTA-wide abort flag and a status word in
 // global memory (read back by fovi_knnconv_check); all roles then drain and leave normally, the
@@ -40,7 +45,10 @@ constexpr int MAX_STAGES = 8;
 constexpr uint32_t A_STAGE_BYTES = 16384;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait attempts before giving up
 
+enum { MODE_C8 = 0, MODE_C64 = 1, MODE_PAIRS = 2 };
+
 struct TcArgs {
+  // per-output-point lists: neighbours (idx, tap) in C8/C64 mode, input pairs (idx only) in PAIRS mode
   const int* nbr_idx; const uint16_t* nbr_tap; const int* nbr_cnt;
   const float* bias; void* Y; int* status;
   int kp, B, n_in, n_out, c_out, cp;
@@ -127,7 +135,7 @@ struct SmemHeader {
   int abort_flag;
 };
 
-template <bool C64>
+template <int MODE>
 __global__ void __launch_bounds__(192, 1)
 fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a) {
   extern __shared__ unsigned char smem_raw[];
@@ -142,7 +150,8 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t b_stage_off = A_STAGE_BYTES;
-  const int chunks = C64 ? a.cp / 64 : a.cp / 8;  // operand boxes per neighbour
+  constexpr bool C64 = MODE == MODE_C64;
+  const int chunks = C64 ? a.cp / 64 : (MODE == MODE_PAIRS ? 1 : a.cp / 8);  // operand boxes per list entry
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.nstage; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
@@ -173,7 +182,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       __syncwarp();
       for (int k = lane; k < a.kp; k += 32) {
         tb_idx[k] = __ldg(a.nbr_idx + (size_t)n * a.kp + k);
-        tb_tap[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
+        if (MODE != MODE_PAIRS) tb_tap[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
       }
       __syncwarp();
       if (lane == 0) {
@@ -190,6 +199,20 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             tma_load_3d(sa + b_stage_off, &tmB, full, cc * 64, o0, tb_tap[k]);
             ++issued;
             if (++cc == chunks) { cc = 0; ++k; }
+            if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+          }
+        } else if (MODE == MODE_PAIRS) {
+          const int steps = (cnt + 7) / 8;
+          for (int st = 0; st < steps; ++st) {
+            const uint32_t full = smem_u32(&hdr->full[s]);
+            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+            mbar_expect_tx(full, a.stage_bytes);
+            const uint32_t sa = stages0 + s * a.stage_bytes;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)  // unused slots hold the out-of-range pair index: zero fill
+              tma_load_3d(sa + j * 2048u, &tmA, full, 0, m0, tb_idx[st * 8 + j]);
+            tma_load_3d(sa + b_stage_off, &tmB, full, 0, o0, n * a.kp + st * 8);  // eight pre-gathered slabs
+            ++issued;
             if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
           }
         } else {
@@ -386,19 +409,20 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   const int ct = pick_cout_tile(p->c_out);
   if (!ct) return FOVI_ERR_UNSUPPORTED;
   const int cp = p->cin_packed;
-  const bool c64 = cp % 64 == 0;
+  const bool c64 = cp % 64 == 0 && p->x_layout != FOVI_X_PAIRS;
 
   TcArgs a;
-  a.nbr_idx = p->nbr_idx; a.nbr_tap = p->nbr_tap; a.nbr_cnt = p->nbr_cnt;
+  const bool pairs = p->x_layout == FOVI_X_PAIRS;
+  a.nbr_idx = pairs ? p->pair_idx : p->nbr_idx; a.nbr_tap = pairs ? nullptr : p->nbr_tap; a.nbr_cnt = pairs ? p->pair_cnt : p->nbr_cnt;
   a.bias = bias; a.Y = Y; a.status = p->status;
-  a.kp = p->kp; a.B = B; a.n_in = p->n_in; a.n_out = p->n_out; a.c_out = p->c_out; a.cp = cp;
+  a.kp = pairs ? p->sp : p->kp; a.B = B; a.n_in = p->n_in; a.n_out = p->n_out; a.c_out = p->c_out; a.cp = cp;
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
   const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
   if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;
   a.stage_bytes = A_STAGE_BYTES + (uint32_t)ct * 128u;
-  a.table_bytes = ((uint32_t)p->kp * 6u + 1023u) & ~1023u;
+  a.table_bytes = ((uint32_t)a.kp * 6u + 1023u) & ~1023u;
   const uint32_t budget = 220u * 1024u - 2048u - a.table_bytes;
   a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
   if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;
@@ -406,19 +430,30 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
 
   CUtensorMap tmA, tmB;
   const uint32_t kc = c64 ? 64 : 8;
-  int rc = encode_3d(&tmA, X, (uint64_t)cp, (uint64_t)p->n_in, (uint64_t)B, (uint64_t)cp * 2, (uint64_t)p->n_in * cp * 2, kc, 1, BM, c64);
-  if (rc) return rc;
-  rc = encode_3d(&tmB, Wt, (uint64_t)cp, (uint64_t)p->c_out, (uint64_t)p->V, (uint64_t)cp * 2, (uint64_t)p->c_out * cp * 2, kc, (uint32_t)ct, 1, c64);
+  int rc;
+  if (pairs) {
+    // A: [n_pairs][B][8] -> box = 128 batch rows of one pair (contiguous 2 KB);  B: [n_out*sp][c_out][8] -> box = 8 slots
+    rc = encode_3d(&tmA, X, 8, (uint64_t)B, (uint64_t)p->n_pairs, 16, (uint64_t)B * 16, 8, BM, 1, false);
+    if (rc) return rc;
+    rc = encode_3d(&tmB, Wt, 8, (uint64_t)p->c_out, (uint64_t)p->n_out * p->sp, 16, (uint64_t)p->c_out * 16, 8, (uint32_t)ct, 8, false);
+  } else {
+    rc = encode_3d(&tmA, X, (uint64_t)cp, (uint64_t)p->n_in, (uint64_t)B, (uint64_t)cp * 2, (uint64_t)p->n_in * cp * 2, kc, 1, BM, c64);
+    if (rc) return rc;
+    rc = encode_3d(&tmB, Wt, (uint64_t)cp, (uint64_t)p->c_out, (uint64_t)p->V, (uint64_t)cp * 2, (uint64_t)p->c_out * cp * 2, kc, (uint32_t)ct, 1, c64);
+  }
   if (rc) return rc;
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = std::min(a.total_items, fovi::sm_count());
-  if (c64) {
-    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fovi_knnconv_tc_kernel<true><<<grid, 192, smem, st>>>(tmA, tmB, a);
+  if (pairs) {
+    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_PAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fovi_knnconv_tc_kernel<MODE_PAIRS><<<grid, 192, smem, st>>>(tmA, tmB, a);
+  } else if (c64) {
+    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_C64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fovi_knnconv_tc_kernel<MODE_C64><<<grid, 192, smem, st>>>(tmA, tmB, a);
   } else {
-    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fovi_knnconv_tc_kernel<false><<<grid, 192, smem, st>>>(tmA, tmB, a);
+    FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_C8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    fovi_knnconv_tc_kernel<MODE_C8><<<grid, 192, smem, st>>>(tmA, tmB, a);
   }
   return fovi::after_launch("fovi_knnconv_tc_kernel");
 }

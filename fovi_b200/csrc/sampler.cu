@@ -39,8 +39,9 @@ struct SampleArgs {
   const float* fix_hw;
   long long sb, sc, sy, sx;  // image element strides
   int B, C, H, W, F, N;
-  int cp;        // channel stride of the points-major layouts
+  int cp;        // channel stride of the points-major layouts (8 = 2 points x 4 channels in pair layout)
   int f_major;   // 1: output row = f*B + b, 0: b*F + f
+  int pairs;     // 1: pair layout [ceil(N/2)][B*F rows][2][4]
 };
 
 template <typename TIn, int PAD>
@@ -59,8 +60,8 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
   const int bf = blockIdx.x;  // b*F + f
   const int b = bf / a.F, f = bf - b * a.F;
   const long long row = a.f_major ? ((long long)f * a.B + b) : (long long)bf;
-  const int row_elems = NC ? a.N * a.cp : a.C * a.N;
-  TOut* out_row = reinterpret_cast<TOut*>(a.out) + row * row_elems;
+  const int row_elems = NC ? (a.pairs ? ((a.N + 1) / 2) * 8 : a.N * a.cp) : a.C * a.N;
+  TOut* out_row = reinterpret_cast<TOut*>(a.out) + (a.pairs ? row * 8 : row * row_elems);
   TOut* dst = STAGE ? stage : out_row;
 
   const float fr = __ldg(a.fix_rc + 2 * bf), fc = __ldg(a.fix_rc + 2 * bf + 1);
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
   const float half_w = __fdiv_rn(fw, 2.f), half_h = __fdiv_rn(fh, 2.f);
   const float sxw = Wf * 0.5f, syh = Hf * 0.5f;  // exact
   const TIn* img_b = reinterpret_cast<const TIn*>(a.img) + (long long)b * a.sb;
+  const int pitch = a.pairs ? 4 : a.cp;  // per-point element pitch of the points-major layouts
 
   if (NC && STAGE) {  // zero the pad channels once
     for (int i = threadIdx.x; i < row_elems; i += blockDim.x) stage[i] = from_float<TOut>(0.f);
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
       const int x = (int)rintf(ix), y = (int)rintf(iy);
       for (int c = 0; c < a.C; ++c) {
         const float v = tap<TIn, PAD>(img_b + c * a.sc, a.sy, a.sx, x, y, a.W, a.H);
-        dst[NC ? (n * a.cp + c) : (c * a.N + n)] = from_float<TOut>(v);
+        dst[NC ? (n * pitch + c) : (c * a.N + n)] = from_float<TOut>(v);
       }
     } else {
       const float x0f = floorf(ix), y0f = floorf(iy);
@@ -113,15 +115,23 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
         acc = __fmaf_rn(v_ne, w_ne, acc);
         acc = __fmaf_rn(v_sw, w_sw, acc);
         acc = __fmaf_rn(v_se, w_se, acc);
-        dst[NC ? (n * a.cp + c) : (c * a.N + n)] = from_float<TOut>(acc);
+        dst[NC ? (n * pitch + c) : (c * a.N + n)] = from_float<TOut>(acc);
       }
     }
     if (NC && !STAGE) {
-      for (int c = a.C; c < a.cp; ++c) dst[n * a.cp + c] = from_float<TOut>(0.f);
+      for (int c = a.C; c < pitch; ++c) dst[n * pitch + c] = from_float<TOut>(0.f);
     }
   }
 
-  if (STAGE) {
+  if (STAGE && NC && a.pairs) {
+    // pair layout: this row owns one 16-byte slot in every pair's block of B*F rows
+    __syncthreads();
+    const long long rows = (long long)a.B * a.F;
+    const int4* s4 = reinterpret_cast<const int4*>(stage);
+    int4* d4 = reinterpret_cast<int4*>(out_row);
+    const int n_pairs = (a.N + 1) / 2;
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) d4[(long long)i * rows] = s4[i];
+  } else if (STAGE) {
     __syncthreads();
     const size_t bytes = (size_t)row_elems * sizeof(TOut);
     const bool vec = ((reinterpret_cast<uintptr_t>(out_row) & 15) == 0) && (bytes % 16 == 0);
@@ -143,6 +153,7 @@ int launch_sample(const SampleArgs& a, size_t stage_bytes, cudaStream_t st) {
     if (stage_bytes > 48 * 1024) FOVI_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_bytes));
     k<<<grid, 512, stage_bytes, st>>>(a);
   } else {
+    if (a.pairs) return FOVI_ERR_UNSUPPORTED;  // the pair layout is only written from the staged row
     fovi_sample_kernel<TIn, TOut, MODE, PAD, NC, false><<<grid, 512, 0, st>>>(a);
   }
   return fovi::after_launch("fovi_sample_kernel");
@@ -150,7 +161,7 @@ int launch_sample(const SampleArgs& a, size_t stage_bytes, cudaStream_t st) {
 
 template <typename TIn, typename TOut, int MODE, int PAD>
 int dispatch_layout(const SampleArgs& a, bool nc, cudaStream_t st) {
-  const size_t stage_bytes = (size_t)(nc ? a.N * a.cp : a.C * a.N) * sizeof(TOut);
+  const size_t stage_bytes = (size_t)(nc ? (a.pairs ? ((a.N + 1) / 2) * 8 : a.N * a.cp) : a.C * a.N) * sizeof(TOut);
   return nc ? launch_sample<TIn, TOut, MODE, PAD, true>(a, stage_bytes, st)
             : launch_sample<TIn, TOut, MODE, PAD, false>(a, stage_bytes, st);
 }
@@ -231,8 +242,12 @@ extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* im
   if (!fovi::valid_dtype(dtype) || !fovi::valid_dtype(out_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   if (mode != FOVI_NEAREST && mode != FOVI_BILINEAR) return FOVI_ERR_INVALID_ARGUMENT;
   if (pad != FOVI_PAD_ZEROS && pad != FOVI_PAD_BORDER) return FOVI_ERR_INVALID_ARGUMENT;
-  if (layout < FOVI_OUT_BFCN || layout > FOVI_OUT_FBNC) return FOVI_ERR_INVALID_ARGUMENT;
-  const bool nc = layout == FOVI_OUT_BFNC || layout == FOVI_OUT_FBNC;
+  if (layout < FOVI_OUT_BFCN || layout > FOVI_OUT_BF_PAIRS) return FOVI_ERR_INVALID_ARGUMENT;
+  const bool pairs = layout == FOVI_OUT_FB_PAIRS || layout == FOVI_OUT_BF_PAIRS;
+  const bool nc = layout == FOVI_OUT_BFNC || layout == FOVI_OUT_FBNC || pairs;
+  if (pairs && (C > 4 || out_dtype != FOVI_BF16)) return FOVI_ERR_UNSUPPORTED;
+  if (pairs) out_channel_stride = 8;
+  if (pairs && (reinterpret_cast<uintptr_t>(out) & 15)) return FOVI_ERR_ALIGNMENT;
   if (nc && out_channel_stride < C) return FOVI_ERR_INVALID_ARGUMENT;
   if ((long long)H * W >= (1ll << 31) || (long long)plan->n_points * (nc ? out_channel_stride : C) >= (1ll << 31))
     return FOVI_ERR_UNSUPPORTED;
@@ -243,7 +258,8 @@ extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* im
   a.sb = img_strides[0]; a.sc = img_strides[1]; a.sy = img_strides[2]; a.sx = img_strides[3];
   a.B = B; a.C = C; a.H = H; a.W = W; a.F = F; a.N = plan->n_points;
   a.cp = nc ? out_channel_stride : C;
-  a.f_major = (layout == FOVI_OUT_FBCN || layout == FOVI_OUT_FBNC) ? 1 : 0;
+  a.f_major = (layout == FOVI_OUT_FBCN || layout == FOVI_OUT_FBNC || layout == FOVI_OUT_FB_PAIRS) ? 1 : 0;
+  a.pairs = pairs ? 1 : 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == FOVI_F32 && out_dtype == FOVI_F32) return dispatch_mode<float, float>(a, mode, pad, nc, st);
   if (dtype == FOVI_F32 && out_dtype == FOVI_BF16) return dispatch_mode<float, __nv_bfloat16>(a, mode, pad, nc, st);

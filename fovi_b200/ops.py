@@ -10,7 +10,8 @@ from ._lib import lib, check
 F32, BF16 = 0, 1
 NEAREST, BILINEAR = 0, 1
 PAD_ZEROS, PAD_BORDER = 0, 1
-OUT_BFCN, OUT_FBCN, OUT_BFNC, OUT_FBNC = 0, 1, 2, 3
+OUT_BFCN, OUT_FBCN, OUT_BFNC, OUT_FBNC, OUT_FB_PAIRS, OUT_BF_PAIRS = 0, 1, 2, 3, 4, 5
+X_BNC, X_PAIRS = 0, 1
 ACT_BCN, ACT_BNC = 0, 1
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
@@ -57,7 +58,8 @@ class SamplerPlan:
 
 def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=None, layout=OUT_BFCN, channel_stride=None, out=None):
     """img [B,C,H,W] (any strides); fix_rc, fix_hw [B,F,2] float32 CUDA.  Returns the sampled
-    tensor in `layout` ([B,F,C,N], [F,B,C,N], [B,F,N,Cp] or [F,B,N,Cp])."""
+    tensor in `layout`: [B,F,C,N], [F,B,C,N], [B,F,N,Cp], [F,B,N,Cp], or the pair layout
+    [ceil(N/2), F*B (or B*F) rows, 8] that a KNNConv plan with c_in <= 4 consumes."""
     _need_cuda(img, fix_rc, fix_hw)
     B, Cc, H, W = img.shape
     fix_rc = fix_rc.to(torch.float32).contiguous()
@@ -66,9 +68,14 @@ def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=No
     assert fix_rc.shape == (B, F, 2) and fix_hw.shape == (B, F, 2)
     out_dtype = img.dtype if out_dtype is None else out_dtype
     nc = layout in (OUT_BFNC, OUT_FBNC)
+    pairs = layout in (OUT_FB_PAIRS, OUT_BF_PAIRS)
     cp = (channel_stride or Cc) if nc else Cc
     lead = (F, B) if layout in (OUT_FBCN, OUT_FBNC) else (B, F)
-    shape = lead + ((plan.n_points, cp) if nc else (Cc, plan.n_points))
+    if pairs:
+        out_dtype, cp = torch.bfloat16, 8
+        shape = ((plan.n_points + 1) // 2, B * F, 8)
+    else:
+        shape = lead + ((plan.n_points, cp) if nc else (Cc, plan.n_points))
     if out is None:
         out = torch.empty(shape, dtype=out_dtype, device=img.device)
     else:
@@ -97,6 +104,8 @@ class KnnConvPlan:
         self._h = h
         self.cin_packed = lib.fovi_knnconv_cin_packed(h)
         self.nnz = lib.fovi_knnconv_nnz(h)
+        self.x_layout = lib.fovi_knnconv_x_layout(h)
+        self.n_pairs = (self.n_in + 1) // 2
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -108,21 +117,34 @@ class KnnConvPlan:
         return 2 * self.c_in * self.c_out * self.nnz
 
     def pack_weights(self, weight, dtype=torch.bfloat16):
-        """weight [c_out, c_in*V] (KNNConvLayer.weight) -> slabs [V, c_out, cin_packed]."""
+        """weight [c_out, c_in*V] (KNNConvLayer.weight) -> packed operand: slabs [V, c_out, cin_packed], or
+        (bf16, pair layout) per-output-point slabs [n_out, pair_slots, c_out, 8]."""
         _need_cuda(weight)
         weight = weight.detach().contiguous()
         assert weight.shape == (self.c_out, self.c_in * self.V)
-        dst = torch.empty((self.V, self.c_out, self.cin_packed), dtype=dtype, device=weight.device)
+        nbytes = lib.fovi_knnconv_packed_weight_bytes(self._h, _dt(dtype))
+        if self.x_layout == X_PAIRS and dtype == torch.bfloat16:
+            dst = torch.empty((self.n_out, nbytes // (self.n_out * self.c_out * 16), self.c_out, 8), dtype=dtype, device=weight.device)
+        else:
+            dst = torch.empty((self.V, self.c_out, self.cin_packed), dtype=dtype, device=weight.device)
+        assert dst.numel() * dst.element_size() == nbytes
         with torch.cuda.device(weight.device):
             check(lib.fovi_knnconv_pack_weights(self._h, _ptr(weight), _dt(weight.dtype), _ptr(dst), _dt(dtype), _stream()), "fovi_knnconv_pack_weights")
         return dst
 
     def forward(self, x_bnc, wt, bias=None, relu=False, out_dtype=torch.bfloat16, out=None):
-        """Tensor-core path.  x_bnc [B,n_in,cin_packed] bf16 contiguous -> [B,n_out,c_out]."""
+        """Tensor-core path.  x_bnc: bf16 contiguous, [B,n_in,cin_packed] or (pair layout)
+        [n_pairs,B,8]  ->  [B,n_out,c_out]."""
         _need_cuda(x_bnc, wt, bias)
-        B = x_bnc.shape[0]
-        assert x_bnc.dtype == torch.bfloat16 and x_bnc.is_contiguous() and x_bnc.shape[1:] == (self.n_in, self.cin_packed), x_bnc.shape
-        assert wt.dtype == torch.bfloat16 and wt.is_contiguous() and wt.shape == (self.V, self.c_out, self.cin_packed)
+        assert x_bnc.dtype == torch.bfloat16 and x_bnc.is_contiguous() and wt.dtype == torch.bfloat16 and wt.is_contiguous()
+        if self.x_layout == X_PAIRS:
+            B = x_bnc.shape[1]
+            assert x_bnc.shape == (self.n_pairs, B, 8), x_bnc.shape
+            assert wt.dim() == 4 and wt.shape[0] == self.n_out and wt.shape[2:] == (self.c_out, 8), wt.shape
+        else:
+            B = x_bnc.shape[0]
+            assert x_bnc.shape[1:] == (self.n_in, self.cin_packed), x_bnc.shape
+            assert wt.shape == (self.V, self.c_out, self.cin_packed)
         if bias is not None:
             bias = bias.detach().to(torch.float32).contiguous()
         if out is None:
@@ -154,14 +176,18 @@ class KnnConvPlan:
             check(lib.fovi_knnconv_check(self._h, _stream()), "fovi_knnconv_check")
 
 
-def pack_points(x, cp):
-    """x [B,C,N] float32/bf16 -> [B,N,cp] bf16, pad channels zero."""
+def pack_points(x, cp=8, x_layout=X_BNC):
+    """x [B,C,N] float32/bf16 -> tensor-core input: [B,N,cp] bf16 (pad channels zero) or the pair
+    layout [ceil(N/2),B,8].  Pass a KnnConvPlan as `cp` to get the layout that plan consumes."""
     _need_cuda(x)
+    if isinstance(cp, KnnConvPlan):
+        cp, x_layout = cp.cin_packed, cp.x_layout
     x = x.contiguous()
     B, Cc, N = x.shape
-    dst = torch.empty((B, N, cp), dtype=torch.bfloat16, device=x.device)
+    shape = ((N + 1) // 2, B, 8) if x_layout == X_PAIRS else (B, N, cp)
+    dst = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
-        check(lib.fovi_pack_points(_ptr(x), _dt(x.dtype), B, Cc, N, _ptr(dst), cp, _stream()), "fovi_pack_points")
+        check(lib.fovi_pack_points(_ptr(x), _dt(x.dtype), B, Cc, N, _ptr(dst), cp, x_layout, _stream()), "fovi_pack_points")
     return dst
 
 

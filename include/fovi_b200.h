@@ -43,8 +43,20 @@ typedef enum {
   FOVI_OUT_FBCN = 1, /* [F,B,C,N]  the '(f b) c n' flattening of fovinet.py:281               */
   FOVI_OUT_BFNC = 2, /* [B,F,N,Cp] points-major, channels last, Cp = out_channel_stride >= C,
                         channels C..Cp-1 written as 0: the KNNConv kernels' input layout      */
-  FOVI_OUT_FBNC = 3  /* [F,B,N,Cp]                                                            */
+  FOVI_OUT_FBNC = 3, /* [F,B,N,Cp]                                                            */
+  FOVI_OUT_FB_PAIRS = 4, /* [ceil(N/2), F*B, 2, 4]: point pairs outermost, then the image x fixation
+                            row (f*B + b), then the two points of the pair with 4 channels each
+                            (channels C..3 and an odd last point written as 0); bf16, C <= 4.
+                            The input layout of a KNNConv plan with c_in <= 4 (FOVI_X_PAIRS).  */
+  FOVI_OUT_BF_PAIRS = 5  /* same with row = b*F + f                                            */
 } fovi_sample_layout;
+
+/* Input layout the tensor-core path of a KNNConv plan expects (fovi_knnconv_x_layout). */
+typedef enum {
+  FOVI_X_BNC = 0,  /* [B, n_in, cin_packed] bf16, channels last                                */
+  FOVI_X_PAIRS = 1 /* [ceil(n_in/2), B, 2, 4] bf16 (see FOVI_OUT_FB_PAIRS); chosen when c_in <= 4:
+                      a neighbour pair of all 128 batch rows is one contiguous 2 KB block        */
+} fovi_x_layout;
 
 /* Activation layouts of KNNConv. */
 typedef enum {
@@ -110,28 +122,34 @@ int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16_t* tap, in
                              int c_in, int c_out, fovi_knnconv_plan** out);
 void fovi_knnconv_plan_destroy(fovi_knnconv_plan* plan);
 
-/* Channel count of the packed bf16 operands: c_in rounded up to a multiple of 8 (64 when
- * c_in > 8 is a multiple of 64 already).  Activations handed to the tensor-core path are
+/* Channel count of the packed bf16 operands: c_in rounded up to a multiple of 8 (kept when it
+ * is a multiple of 64).  With FOVI_X_BNC, activations handed to the tensor-core path are
  * [B,n_in,cin_packed] bf16 with channels c_in..cin_packed-1 equal to 0. */
 int fovi_knnconv_cin_packed(const fovi_knnconv_plan* plan);
+/* FOVI_X_BNC or FOVI_X_PAIRS (c_in <= 4). */
+int fovi_knnconv_x_layout(const fovi_knnconv_plan* plan);
 /* Number of non-pad (n,k) entries: algorithmic FLOPs per image = 2*c_in*c_out*nnz. */
 int64_t fovi_knnconv_nnz(const fovi_knnconv_plan* plan);
 
-/* Repack KNNConvLayer.weight ([c_out, c_in*V], c-major/v-minor, knn.py:462) into V slabs
- * [V, c_out, cin_packed] of `dst_dtype` (bf16 for the tensor-core path, f32 for the exact
- * path), zero-filling the padded channels.  W, dst: device pointers. */
+/* Repack KNNConvLayer.weight ([c_out, c_in*V], c-major/v-minor, knn.py:462) for the kernels.
+ * dst_dtype f32 (exact path) or bf16 with FOVI_X_BNC: V slabs [V, c_out, cin_packed], padded
+ * channels zero.  dst_dtype bf16 with FOVI_X_PAIRS: per output point the slabs of its own
+ * neighbour pairs, [n_out, pair_slots, c_out, 8] (the reference's local_rf applied to the weights,
+ * knn.py:528-536, in bf16); slots or pair halves without a neighbour are zero.
+ * W, dst: device pointers; size from fovi_knnconv_packed_weight_bytes. */
 int fovi_knnconv_pack_weights(const fovi_knnconv_plan* plan, const void* W, int w_dtype, void* dst, int dst_dtype,
                               void* stream);
 /* Bytes of the packed weight buffer for `dst_dtype`. */
 int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* plan, int dst_dtype);
 
-/* Convert activations [B,C,N] (x_dtype, contiguous) to the packed points-major layout
- * [B,N,cp] bf16 with zero-filled pad channels (cp >= C, multiple of 8). */
-int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, void* stream);
+/* Convert activations [B,C,N] (x_dtype, contiguous) to a tensor-core input layout:
+ * x_layout FOVI_X_BNC: [B,N,cp] bf16 with zero-filled pad channels (cp >= C, multiple of 8);
+ * x_layout FOVI_X_PAIRS: [ceil(N/2),B,2,4] bf16 (C <= 4; cp ignored). */
+int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, int x_layout, void* stream);
 
 /* Tensor-core path (tcgen05 MMA, bf16 operands, fp32 accumulation in tensor memory).
- * X    : [B,n_in,cin_packed] bf16, 16-byte aligned.
- * Wt   : packed bf16 slabs from fovi_knnconv_pack_weights.
+ * X    : bf16 in the plan's input layout (fovi_knnconv_x_layout), 16-byte aligned.
+ * Wt   : packed bf16 weights from fovi_knnconv_pack_weights.
  * bias : [c_out] float32 or NULL.
  * Y    : [B,n_out,c_out] of y_dtype (bf16 or f32), 16-byte aligned; c_out % 8 == 0.
  * relu : apply max(.,0) after the bias.

@@ -37,7 +37,7 @@ def bf16_round(a):
 
 def run_tc(ops, plan, x_bcn, w, bias=None, relu=False, out_dtype=torch.float32):
     wt = plan.pack_weights(dev(w))
-    xp = ops.pack_points(dev(x_bcn), plan.cin_packed)
+    xp = ops.pack_points(dev(x_bcn), plan)
     y = plan.forward(xp, wt, None if bias is None else dev(bias), relu=relu, out_dtype=out_dtype)
     plan.check()
     return y.to(torch.float32).permute(0, 2, 1).cpu().numpy()
@@ -65,7 +65,7 @@ def test_config1_tensor_core_path(ops, golden):
     V = int(g["V"])
     w = kaiming_weight(np.random.RandomState(1), 64, 3, V)
     plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), V, 3, 64)
-    assert plan.cin_packed == 8
+    assert plan.cin_packed == 8 and plan.x_layout == ops.X_PAIRS
     y = run_tc(ops, plan, g["sampled"], w)
     assert rel_l2(y[0], g["conv_out_b0"]) < BF16_TOL
     # against the oracle on bf16-rounded operands the only difference is fp32 summation order
@@ -79,11 +79,13 @@ def test_config3_stack_tensor_core(ops, golden):
     chans = [3, 64, 192, 384, 256, 256]
     rs = np.random.RandomState(1)
     x = synth_images(0, (2, 3, 4010))
-    h = ops.pack_points(dev(x), 8)
+    h = None
     for i in range(5):
         V = int(t[f"l{i}_V"])
         w = kaiming_weight(rs, chans[i + 1], chans[i], V)
         plan = ops.KnnConvPlan(t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"], int(t[f"l{i}_n_in"]), V, chans[i], chans[i + 1])
+        if h is None:
+            h = ops.pack_points(dev(x), plan)
         wt = plan.pack_weights(dev(w))
         h = plan.forward(h, wt, torch.zeros(chans[i + 1], device="cuda"), relu=i < 4, out_dtype=torch.bfloat16)
         plan.check()
@@ -108,7 +110,9 @@ def test_config4_patch_embed(ops, golden, tag):
 
 
 @pytest.mark.parametrize("B,Cin,Nin,Nout,K,V,Cout", [
-    (1, 3, 40, 17, 5, 9, 16),        # one image, tiny tables, smallest c_out tile
+    (1, 3, 40, 17, 5, 9, 16),        # one image, tiny tables, smallest c_out tile (pair layout; repeated neighbours)
+    (131, 1, 37, 9, 12, 7, 32),      # one channel, odd point count, ragged second batch tile (pair layout)
+    (3, 4, 64, 10, 40, 50, 64),      # four channels, more pair slots than one stage (pair layout)
     (130, 8, 33, 9, 4, 4, 32),       # batch spills into a second, ragged batch tile
     (5, 64, 50, 21, 9, 36, 64),      # 64-channel swizzled operand path
     (3, 128, 30, 11, 7, 16, 384),    # two channel chunks, two c_out tiles of 192
@@ -159,6 +163,6 @@ def test_linearity_and_determinism_full_batch(ops, golden):
 def test_empty_batch(ops, golden):
     g = golden("config4_patch_embed_p8.npz")
     plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), int(g["V"]), 3, 384)
-    wt = torch.zeros((int(g["V"]), 384, 8), dtype=torch.bfloat16, device="cuda")
-    y = plan.forward(torch.empty((0, int(g["n_in"]), 8), dtype=torch.bfloat16, device="cuda"), wt)
+    wt = plan.pack_weights(torch.zeros((384, 3 * int(g["V"])), device="cuda"))
+    y = plan.forward(torch.empty((plan.n_pairs, 0, 8), dtype=torch.bfloat16, device="cuda"), wt)
     assert y.shape == (0, plan.n_out, 384)
