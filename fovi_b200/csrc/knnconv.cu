@@ -19,16 +19,23 @@ __global__ void pack_weights_kernel(const TW* __restrict__ W, TD* __restrict__ d
   }
 }
 
-// Pair mode: W [c_out, c_in*V] -> per-output-point slabs [n_out, sp, c_out, 8]; element (h, c) of a
-// slot row is the weight of channel c (< 4) for the even (h = 0) or odd (h = 1) point of the pair.
+// Pair mode: W [c_out, c_in*V] -> per-output-point slabs [n_out, c_out/ct, sp, ct, 8] (so the eight
+// slots of one stage of one c_out tile are contiguous); element (h, c) of a slot row is the weight
+// of channel c (< 4) for the even (h = 0) or odd (h = 1) point of the pair.
 template <typename TW>
 __global__ void pack_weights_pairs_kernel(const TW* __restrict__ W, __nv_bfloat16* __restrict__ dst,
-                                          const uint16_t* __restrict__ pair_tap, int n_out, int sp, int V, int c_out, int c_in) {
+                                          const uint16_t* __restrict__ pair_tap, int n_out, int sp, int V, int c_out, int c_in, int ct) {
   const long long total = (long long)n_out * sp * c_out * 8;
+  const int n_ct = c_out / ct;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int e = (int)(i & 7);
-    const int o = (int)((i >> 3) % c_out);
-    const long long slot = (i >> 3) / c_out;  // n*sp + s
+    long long r = i >> 3;
+    const int oc = (int)(r % ct); r /= ct;
+    const int sl = (int)(r % sp); r /= sp;
+    const int tile = (int)(r % n_ct);
+    const long long n = r / n_ct;
+    const int o = tile * ct + oc;
+    const long long slot = n * sp + sl;
     const int h = e >> 2, c = e & 3;
     const int t = pair_tap[slot * 2 + h];
     const float w = (c < c_in && t != 0xFFFF) ? ld_as_float(W + ((long long)o * c_in + c) * V + t) : 0.f;
@@ -133,6 +140,7 @@ extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16
   auto* p = new fovi_knnconv_plan();
   p->n_in = n_in; p->n_out = n_out; p->K = K; p->V = V; p->c_in = c_in; p->c_out = c_out; p->kp = kp; p->nnz = nnz;
   p->cin_packed = (c_in % 64 == 0) ? c_in : (c_in + 7) / 8 * 8;
+  p->ct = (c_out % 16 == 0) ? fovi::pick_cout_tile(c_out) : 0;
   // Pair mode for tiny channel counts: group each point's neighbours into aligned input pairs
   // (2p, 2p+1).  A neighbour takes the free half of a slot of its pair, or opens a new slot (so a
   // table that lists the same input point twice still adds both taps).
@@ -179,6 +187,8 @@ extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16
     e = cudaMalloc(&p->pair_idx, sizeof(int) * pidx.size());
     if (e == cudaSuccess) e = cudaMalloc(&p->pair_cnt, sizeof(int) * n_out);
     if (e == cudaSuccess) e = cudaMalloc(&p->pair_tap, sizeof(uint16_t) * ptap.size());
+    if (e == cudaSuccess) e = cudaMalloc(&p->zero_block, 2048);
+    if (e == cudaSuccess) e = cudaMemset(p->zero_block, 0, 2048);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_idx, pidx.data(), sizeof(int) * pidx.size(), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_cnt, pcnt.data(), sizeof(int) * n_out, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_tap, ptap.data(), sizeof(uint16_t) * ptap.size(), cudaMemcpyHostToDevice);
@@ -208,6 +218,7 @@ extern "C" void fovi_knnconv_plan_destroy(fovi_knnconv_plan* p) {
   if (p->pair_idx) cudaFree(p->pair_idx);
   if (p->pair_cnt) cudaFree(p->pair_cnt);
   if (p->pair_tap) cudaFree(p->pair_tap);
+  if (p->zero_block) cudaFree(p->zero_block);
   delete p;
 }
 
@@ -226,12 +237,13 @@ extern "C" int fovi_knnconv_pack_weights(const fovi_knnconv_plan* p, const void*
   if (!p || !W || !dst || !fovi::valid_dtype(w_dtype) || !fovi::valid_dtype(dst_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (p->x_layout == FOVI_X_PAIRS && dst_dtype == FOVI_BF16) {
+    if (!p->ct) return FOVI_ERR_UNSUPPORTED;
     const long long tot = (long long)p->n_out * p->sp * p->c_out * 8;
     const int g = (int)std::min<long long>((tot + 255) / 256, 148 * 32);
     if (w_dtype == FOVI_F32)
-      pack_weights_pairs_kernel<float><<<g, 256, 0, st>>>((const float*)W, (__nv_bfloat16*)dst, p->pair_tap, p->n_out, p->sp, p->V, p->c_out, p->c_in);
+      pack_weights_pairs_kernel<float><<<g, 256, 0, st>>>((const float*)W, (__nv_bfloat16*)dst, p->pair_tap, p->n_out, p->sp, p->V, p->c_out, p->c_in, p->ct);
     else
-      pack_weights_pairs_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)W, (__nv_bfloat16*)dst, p->pair_tap, p->n_out, p->sp, p->V, p->c_out, p->c_in);
+      pack_weights_pairs_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)W, (__nv_bfloat16*)dst, p->pair_tap, p->n_out, p->sp, p->V, p->c_out, p->c_in, p->ct);
     return fovi::after_launch("pack_weights_pairs_kernel");
   }
   const long long total = (long long)p->V * p->c_out * p->cin_packed;

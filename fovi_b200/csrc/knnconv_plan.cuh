@@ -2,6 +2,18 @@
 #pragma once
 #include "common.cuh"
 
+namespace fovi {
+// Largest c_out tile <= 256 that divides c_out and is a multiple of 16 (0 if none).
+inline int pick_cout_tile(int c_out) {
+  for (int n_ct = 1; n_ct <= c_out / 16; ++n_ct) {
+    if (c_out % n_ct) continue;
+    const int ct = c_out / n_ct;
+    if (ct <= 256 && ct % 16 == 0) return ct;
+  }
+  return 0;
+}
+}  // namespace fovi
+
 struct fovi_knnconv_plan {
   int n_in = 0, n_out = 0, K = 0, V = 0, c_in = 0, c_out = 0;
   int cin_packed = 0;  // channel count of the packed bf16/f32 operands
@@ -21,4 +33,6 @@ struct fovi_knnconv_plan {
   int* pair_idx = nullptr;      // [n_out, sp] pair index; unused slots hold n_pairs (reads as zero)
   int* pair_cnt = nullptr;      // [n_out]
   uint16_t* pair_tap = nullptr; // [n_out, sp, 2] tap of the even / odd member, 0xFFFF = not a neighbour
+  void* zero_block = nullptr;   // 2 KB of zeros: the operand block read for unused pair slots
+  int ct = 0;                   // c_out tile of the tensor-core path (UMMA N), 0 = unsupported c_out
 };

@@ -26,15 +26,19 @@
 //          boxes.  Tail boxes read the out-of-range point index n_in, which TMA fills with zeros;
 //   PAIRS  c_in <= 4 (RGB first layers, patch embeddings): activations are stored pair-major,
 //          [point pair][batch row][2 points x 4 channels], so the 128 batch rows of one pair are
-//          ONE contiguous 2 KB block (a 16-byte-row box like C8, but 16x fewer memory rows than
-//          gathering 128 strided rows), and the weights are pre-gathered per output point so the
-//          eight slabs of a stage are one contiguous box.  One MMA (K=16) consumes two pairs =
-//          four neighbours.
+//          ONE contiguous 2 KB block that already is the un-swizzled core-matrix layout, and the
+//          weights are pre-gathered per output point and c_out tile so the eight slabs of a stage
+//          are one contiguous block too.  Both move with plain bulk copies (cp.async.bulk): TMA
+//          handles a box of 16-byte rows one row at a time, a contiguous block at full width.
+//          One MMA (K=16) consumes two pairs = four neighbours.  Unused slots read a block of
+//          zeros; rows past the batch keep stale shared memory, which only reaches output rows
+//          that are never stored.
 //
 // Every wait is bounded: a wait that gives up raises a CTA-wide abort flag and a status word in
 // global memory (read back by fovi_knnconv_check); all roles then drain and leave normally, the
 // tensor memory is freed and the context stays usable.
 #include <cuda.h>
+#include <string.h>
 
 #include "knnconv_plan.cuh"
 
@@ -53,6 +57,7 @@ struct TcArgs {
   const float* bias; void* Y; int* status;
   int kp, B, n_in, n_out, c_out, cp;
   int ct, n_ct, n_mt, nstage, relu, y_f32, total_items;
+  const unsigned char* X; const unsigned char* Wt; const unsigned char* zero_block; int n_pairs;  // PAIRS mode
   uint32_t stage_bytes, table_bytes;
 };
 
@@ -90,6 +95,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+
+// Contiguous global -> shared bulk copy (16-byte aligned, size a multiple of 16).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -203,15 +214,20 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           }
         } else if (MODE == MODE_PAIRS) {
           const int steps = (cnt + 7) / 8;
+          const uint32_t a_bytes = (uint32_t)min(BM, a.B - m0) * 16u, b_bytes = 8u * (uint32_t)a.ct * 16u;
+          const unsigned char* wn = a.Wt + ((size_t)n * a.n_ct + ctile) * a.kp * ((size_t)a.ct * 16);
           for (int st = 0; st < steps; ++st) {
             const uint32_t full = smem_u32(&hdr->full[s]);
             if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
-            mbar_expect_tx(full, a.stage_bytes);
+            mbar_expect_tx(full, 8u * a_bytes + b_bytes);
             const uint32_t sa = stages0 + s * a.stage_bytes;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)  // unused slots hold the out-of-range pair index: zero fill
-              tma_load_3d(sa + j * 2048u, &tmA, full, 0, m0, tb_idx[st * 8 + j]);
-            tma_load_3d(sa + b_stage_off, &tmB, full, 0, o0, n * a.kp + st * 8);  // eight pre-gathered slabs
+            for (int j = 0; j < 8; ++j) {
+              const int pr = tb_idx[st * 8 + j];
+              const unsigned char* src = pr < a.n_pairs ? a.X + ((size_t)pr * a.B + m0) * 16 : a.zero_block;
+              bulk_load(sa + j * 2048u, src, a_bytes, full);
+            }
+            bulk_load(sa + b_stage_off, wn + (size_t)st * b_bytes, b_bytes, full);  // eight pre-gathered slabs
             ++issued;
             if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
           }
@@ -387,16 +403,6 @@ int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_
   return FOVI_OK;
 }
 
-// Largest c_out tile <= 256 that divides c_out and is a multiple of 16.
-int pick_cout_tile(int c_out) {
-  for (int n_ct = 1; n_ct <= c_out / 16; ++n_ct) {
-    if (c_out % n_ct) continue;
-    const int ct = c_out / n_ct;
-    if (ct <= 256 && ct % 16 == 0) return ct;
-  }
-  return 0;
-}
-
 }  // namespace
 
 extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
@@ -406,7 +412,7 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   if (!X || !Wt || !Y) return FOVI_ERR_INVALID_ARGUMENT;
   if (p->c_out % 16) return FOVI_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Wt) | reinterpret_cast<uintptr_t>(Y)) & 15) return FOVI_ERR_ALIGNMENT;
-  const int ct = pick_cout_tile(p->c_out);
+  const int ct = p->ct;
   if (!ct) return FOVI_ERR_UNSUPPORTED;
   const int cp = p->cin_packed;
   const bool c64 = cp % 64 == 0 && p->x_layout != FOVI_X_PAIRS;
@@ -431,11 +437,12 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   CUtensorMap tmA, tmB;
   const uint32_t kc = c64 ? 64 : 8;
   int rc;
+  a.X = static_cast<const unsigned char*>(X); a.Wt = static_cast<const unsigned char*>(Wt);
+  a.zero_block = static_cast<const unsigned char*>(p->zero_block); a.n_pairs = p->n_pairs;
   if (pairs) {
-    // A: [n_pairs][B][8] -> box = 128 batch rows of one pair (contiguous 2 KB);  B: [n_out*sp][c_out][8] -> box = 8 slots
-    rc = encode_3d(&tmA, X, 8, (uint64_t)B, (uint64_t)p->n_pairs, 16, (uint64_t)B * 16, 8, BM, 1, false);
-    if (rc) return rc;
-    rc = encode_3d(&tmB, Wt, 8, (uint64_t)p->c_out, (uint64_t)p->n_out * p->sp, 16, (uint64_t)p->c_out * 16, 8, (uint32_t)ct, 8, false);
+    // operands move with plain bulk copies; the tensor maps are unused placeholders
+    memset(&tmA, 0, sizeof(tmA)); memset(&tmB, 0, sizeof(tmB));
+    rc = FOVI_OK;
   } else {
     rc = encode_3d(&tmA, X, (uint64_t)cp, (uint64_t)p->n_in, (uint64_t)B, (uint64_t)cp * 2, (uint64_t)p->n_in * cp * 2, kc, 1, BM, c64);
     if (rc) return rc;

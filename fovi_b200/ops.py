@@ -124,7 +124,7 @@ class KnnConvPlan:
         assert weight.shape == (self.c_out, self.c_in * self.V)
         nbytes = lib.fovi_knnconv_packed_weight_bytes(self._h, _dt(dtype))
         if self.x_layout == X_PAIRS and dtype == torch.bfloat16:
-            dst = torch.empty((self.n_out, nbytes // (self.n_out * self.c_out * 16), self.c_out, 8), dtype=dtype, device=weight.device)
+            dst = torch.empty((self.n_out, nbytes // (self.n_out * self.c_out * 16), self.c_out, 8), dtype=dtype, device=weight.device)  # memory order [n_out, c_out tiles, slots, tile, 8]
         else:
             dst = torch.empty((self.V, self.c_out, self.cin_packed), dtype=dtype, device=weight.device)
         assert dst.numel() * dst.element_size() == nbytes
