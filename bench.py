@@ -186,7 +186,7 @@ def main():
     hw = torch.full((B, F, 2), 256.0, device=dev)
     x_dev = x_host.to(dev); fix_dev = fix_host.to(dev)
     # preallocated activations (channels-last points layout), reused every step
-    acts = [torch.empty(((splan.n_points + 1) // 2, M, 8), dtype=torch.bfloat16, device=dev)]   # pair layout
+    acts = [torch.zeros(((M + 127) // 128, (splan.n_points + 1) // 2, 128, 8), dtype=torch.bfloat16, device=dev)]   # pair layout
     for i in range(5):
         acts.append(torch.empty((M, plans[i].n_out, CHANS[i + 1]), dtype=torch.bfloat16, device=dev))
     out_host = torch.empty(acts[-1].shape, dtype=torch.bfloat16).pin_memory()
@@ -201,7 +201,7 @@ def main():
         ops.sample(splan, x, fix, hw, layout=ops.OUT_FB_PAIRS, out=acts[0])
         if marks: marks[1].record()
         for i in range(5):
-            plans[i].forward(acts[i], wts[i], biases[i], relu=i < 4, out=acts[i + 1])
+            plans[i].forward(acts[i], wts[i], biases[i], relu=i < 4, out=acts[i + 1], batch=M)
             if marks: marks[i + 2].record()
         if marks: record.append(marks)
         return acts[-1]

@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libfovi_b200.so")
+# FOVI_B200_LIBRARY points at another build of the same ABI (e.g. a debug build); default: in-tree.
+LIB_PATH = os.environ.get("FOVI_B200_LIBRARY") or os.path.join(HERE, "libfovi_b200.so")
 
 # name -> (restype, argtypes); must list every symbol the header declares.
 _P = C.c_void_p

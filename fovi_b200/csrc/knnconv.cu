@@ -43,7 +43,7 @@ __global__ void pack_weights_pairs_kernel(const TW* __restrict__ W, __nv_bfloat1
   }
 }
 
-// X [B,C,N] -> [ceil(N/2), B, 2, 4] bf16 (pair layout), one thread per (pair, image).
+// X [B,C,N] -> [ceil(B/128), ceil(N/2), 128, 2, 4] bf16 (pair layout), one thread per (pair, image).
 template <typename TX>
 __global__ void pack_points_pairs_kernel(const TX* __restrict__ x, __nv_bfloat16* __restrict__ dst, int B, int C, int N) {
   const int n_pairs = (N + 1) / 2;
@@ -58,7 +58,7 @@ __global__ void pack_points_pairs_kernel(const TX* __restrict__ x, __nv_bfloat16
         const int n = 2 * pr + h;
         v[h * 4 + c] = __float2bfloat16_rn((c < C && n < N) ? ld_as_float(x + ((long long)b * C + c) * N + n) : 0.f);
       }
-    *reinterpret_cast<uint4*>(dst + ((long long)pr * B + b) * 8) = *reinterpret_cast<const uint4*>(v);
+    *reinterpret_cast<uint4*>(dst + (((long long)(b >> 7) * n_pairs + pr) * 128 + (b & 127)) * 8) = *reinterpret_cast<const uint4*>(v);
   }
 }
 
@@ -187,8 +187,8 @@ extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16
     e = cudaMalloc(&p->pair_idx, sizeof(int) * pidx.size());
     if (e == cudaSuccess) e = cudaMalloc(&p->pair_cnt, sizeof(int) * n_out);
     if (e == cudaSuccess) e = cudaMalloc(&p->pair_tap, sizeof(uint16_t) * ptap.size());
-    if (e == cudaSuccess) e = cudaMalloc(&p->zero_block, 2048);
-    if (e == cudaSuccess) e = cudaMemset(p->zero_block, 0, 2048);
+    if (e == cudaSuccess) e = cudaMalloc(&p->zero_block, 16384);
+    if (e == cudaSuccess) e = cudaMemset(p->zero_block, 0, 16384);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_idx, pidx.data(), sizeof(int) * pidx.size(), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_cnt, pcnt.data(), sizeof(int) * n_out, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_tap, ptap.data(), sizeof(uint16_t) * ptap.size(), cudaMemcpyHostToDevice);

@@ -146,6 +146,15 @@ struct SmemHeader {
   int abort_flag;
 };
 
+constexpr int TBQ = 8;  // table entries prefetched per producer lane: list pitch <= 32 * TBQ
+
+__device__ __forceinline__ void decode_item(const TcArgs& a, int item, int& n, int& mt, int& ctile) {
+  ctile = item % a.n_ct;
+  const int t = item / a.n_ct;
+  n = t % a.n_out;
+  mt = t / a.n_out;
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(192, 1)
 fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a) {
@@ -154,8 +163,10 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* basep = smem_raw + (base - raw);
   SmemHeader* hdr = reinterpret_cast<SmemHeader*>(basep);
-  int* tb_idx = reinterpret_cast<int*>(basep + 1024);
-  uint16_t* tb_tap = reinterpret_cast<uint16_t*>(basep + 1024 + (size_t)a.kp * 4);
+  // two table buffers (the next item's list is prefetched while the current one is issued), then the bias
+  const uint32_t tbl_pitch = ((uint32_t)a.kp * 6u + 15u) & ~15u;
+  unsigned char* tbl0 = basep + 1024;
+  float* bias_s = reinterpret_cast<float*>(basep + 1024 + 2 * tbl_pitch);
   const uint32_t stages0 = base + 1024u + a.table_bytes;  // 1024-aligned
   volatile int* abort_flag = &hdr->abort_flag;
 
@@ -171,6 +182,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  for (int i = threadIdx.x; i < a.c_out; i += blockDim.x) bias_s[i] = a.bias ? __ldg(a.bias + i) : 0.f;
   if (warp == 1) {  // allocate all 512 tensor-memory columns: two accumulators of up to 256
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&hdr->tmem_base)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -185,17 +197,39 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     uint32_t s = 0, ph = 0;
     uint32_t issued = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
-      const int ctile = item % a.n_ct;
-      const int t = item / a.n_ct;
-      const int n = t % a.n_out, mt = t / a.n_out;
-      const int cnt = __ldg(a.nbr_cnt + n);
-      __syncwarp();
+    int item = blockIdx.x, buf = 0, cnt = 0;
+    if (item < a.total_items) {  // first item's list straight into buffer 0
+      int n, mt, ctile;
+      decode_item(a, item, n, mt, ctile);
+      int* ti = reinterpret_cast<int*>(tbl0);
+      uint16_t* tt = reinterpret_cast<uint16_t*>(tbl0 + (size_t)a.kp * 4);
       for (int k = lane; k < a.kp; k += 32) {
-        tb_idx[k] = __ldg(a.nbr_idx + (size_t)n * a.kp + k);
-        if (MODE != MODE_PAIRS) tb_tap[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
+        ti[k] = __ldg(a.nbr_idx + (size_t)n * a.kp + k);
+        if (MODE != MODE_PAIRS) tt[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
       }
-      __syncwarp();
+      cnt = __ldg(a.nbr_cnt + n);
+    }
+    __syncwarp();
+    while (item < a.total_items && ok) {
+      const int next = item + gridDim.x;
+      int n, mt, ctile;
+      decode_item(a, item, n, mt, ctile);
+      // prefetch the next item's list into registers: the loads are in flight while lane 0 issues copies
+      int r_idx[TBQ], cnt_next = 0;
+      uint16_t r_tap[TBQ];
+      if (next < a.total_items) {
+        int n2, mt2, ct2;
+        decode_item(a, next, n2, mt2, ct2);
+#pragma unroll
+        for (int q = 0; q < TBQ; ++q) {
+          const int k = lane + 32 * q;
+          r_idx[q] = k < a.kp ? __ldg(a.nbr_idx + (size_t)n2 * a.kp + k) : 0;
+          r_tap[q] = (MODE != MODE_PAIRS && k < a.kp) ? __ldg(a.nbr_tap + (size_t)n2 * a.kp + k) : (uint16_t)0;
+        }
+        cnt_next = __ldg(a.nbr_cnt + n2);
+      }
+      const int* tb_idx = reinterpret_cast<const int*>(tbl0 + buf * tbl_pitch);
+      const uint16_t* tb_tap = reinterpret_cast<const uint16_t*>(tbl0 + buf * tbl_pitch + (size_t)a.kp * 4);
       if (lane == 0) {
         const int m0 = mt * BM, o0 = ctile * a.ct;
         if (C64) {
@@ -214,18 +248,26 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           }
         } else if (MODE == MODE_PAIRS) {
           const int steps = (cnt + 7) / 8;
-          const uint32_t a_bytes = (uint32_t)min(BM, a.B - m0) * 16u, b_bytes = 8u * (uint32_t)a.ct * 16u;
+          const uint32_t b_bytes = 8u * (uint32_t)a.ct * 16u;
           const unsigned char* wn = a.Wt + ((size_t)n * a.n_ct + ctile) * a.kp * ((size_t)a.ct * 16);
+          const unsigned char* xt = a.X + (size_t)mt * a.n_pairs * 2048;  // this batch tile's pair blocks
           for (int st = 0; st < steps; ++st) {
             const uint32_t full = smem_u32(&hdr->full[s]);
             if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
-            mbar_expect_tx(full, 8u * a_bytes + b_bytes);
+            mbar_expect_tx(full, a.stage_bytes);
             const uint32_t sa = stages0 + s * a.stage_bytes;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int pr = tb_idx[st * 8 + j];
-              const unsigned char* src = pr < a.n_pairs ? a.X + ((size_t)pr * a.B + m0) * 16 : a.zero_block;
-              bulk_load(sa + j * 2048u, src, a_bytes, full);
+            const int* sl = tb_idx + st * 8;
+            int j = 0;
+            while (j < 8) {  // the slots are sorted by pair index: copy each run of consecutive pairs at once
+              const int pr = sl[j];
+              if (pr >= a.n_pairs) {  // unused tail slots
+                bulk_load(sa + j * 2048u, a.zero_block, (uint32_t)(8 - j) * 2048u, full);
+                break;
+              }
+              int len = 1;
+              while (j + len < 8 && sl[j + len] == pr + len && pr + len < a.n_pairs) ++len;
+              bulk_load(sa + j * 2048u, xt + (size_t)pr * 2048, (uint32_t)len * 2048u, full);
+              j += len;
             }
             bulk_load(sa + b_stage_off, wn + (size_t)st * b_bytes, b_bytes, full);  // eight pre-gathered slabs
             ++issued;
@@ -252,7 +294,19 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           }
         }
       }
+      __syncwarp();
+      if (next < a.total_items) {  // park the prefetched list in the other buffer
+        int* ti = reinterpret_cast<int*>(tbl0 + (buf ^ 1) * tbl_pitch);
+        uint16_t* tt = reinterpret_cast<uint16_t*>(tbl0 + (buf ^ 1) * tbl_pitch + (size_t)a.kp * 4);
+#pragma unroll
+        for (int q = 0; q < TBQ; ++q) {
+          const int k = lane + 32 * q;
+          if (k < a.kp) { ti[k] = r_idx[q]; if (MODE != MODE_PAIRS) tt[k] = r_tap[q]; }
+        }
+      }
+      __syncwarp();
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      buf ^= 1; cnt = cnt_next; item = next;
     }
     if (lane == 0 && *abort_flag) {
       // Drain: wait (bounded, errors ignored) for the loads this thread armed and nobody consumed.
@@ -270,9 +324,10 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.ct >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t s = 0, ph = 0, acc = 0, aph = 0;
       bool ok = true;
+      int cnt = blockIdx.x < a.total_items ? __ldg(a.nbr_cnt + (blockIdx.x / a.n_ct) % a.n_out) : 0;
       for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
-        const int n = (item / a.n_ct) % a.n_out;
-        const int cnt = __ldg(a.nbr_cnt + n);
+        const int next = item + gridDim.x;
+        const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;  // consumed next round
         const int steps = C64 ? cnt * chunks : (cnt * chunks + 7) / 8;
         if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
         tc_fence_after();
@@ -299,6 +354,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         if (!ok) break;
         tc_commit(smem_u32(&hdr->acc_full[acc]));  // accumulator complete
         if (++acc == 2) { acc = 0; aph ^= 1u; }
+        cnt = cnt_next;
       }
       if (*abort_flag) {  // make sure no MMA is still reading shared memory / writing tensor memory
         tc_commit(smem_u32(&hdr->drain));
@@ -311,11 +367,12 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t acc = 0, aph = 0;
     bool ok = true;
+    int cnt = blockIdx.x < a.total_items ? __ldg(a.nbr_cnt + (blockIdx.x / a.n_ct) % a.n_out) : 0;
     for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
-      const int ctile = item % a.n_ct;
-      const int t = item / a.n_ct;
-      const int n = t % a.n_out, mt = t / a.n_out;
-      const int cnt = __ldg(a.nbr_cnt + n);
+      int n, mt, ctile;
+      decode_item(a, item, n, mt, ctile);
+      const int next = item + gridDim.x;
+      const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;
       ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave as a whole warp or not at all
       if (!ok) break;
@@ -331,8 +388,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         float v[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float x = cnt > 0 ? __uint_as_float(r[i]) : 0.f;
-          if (a.bias) x += __ldg(a.bias + o0 + c0 + i);
+          const float x = (cnt > 0 ? __uint_as_float(r[i]) : 0.f) + bias_s[o0 + c0 + i];
           v[i] = a.relu ? fmaxf(x, 0.f) : x;
         }
         if (row < a.B) {
@@ -356,6 +412,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       tc_fence_before();
       mbar_arrive(smem_u32(&hdr->acc_empty[acc]));
       if (++acc == 2) { acc = 0; aph ^= 1u; }
+      cnt = cnt_next;
     }
   }
 
@@ -427,8 +484,9 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
   if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;
-  a.stage_bytes = A_STAGE_BYTES + (uint32_t)ct * 128u;
-  a.table_bytes = ((uint32_t)a.kp * 6u + 1023u) & ~1023u;
+  a.stage_bytes = A_STAGE_BYTES + (uint32_t)ct * 128u;  // A: 128 rows x 128 B;  B: ct rows x 128 B (any mode)
+  if (a.kp > 32 * TBQ) return FOVI_ERR_UNSUPPORTED;  // neighbour lists longer than 256 entries
+  a.table_bytes = (2u * (((uint32_t)a.kp * 6u + 15u) & ~15u) + (uint32_t)p->c_out * 4u + 1023u) & ~1023u;
   const uint32_t budget = 220u * 1024u - 2048u - a.table_bytes;
   a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
   if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;

@@ -41,7 +41,7 @@ struct SampleArgs {
   int B, C, H, W, F, N;
   int cp;        // channel stride of the points-major layouts (8 = 2 points x 4 channels in pair layout)
   int f_major;   // 1: output row = f*B + b, 0: b*F + f
-  int pairs;     // 1: pair layout [ceil(N/2)][B*F rows][2][4]
+  int pairs;     // 1: pair layout [ceil(rows/128)][ceil(N/2)][128 rows][2][4]
 };
 
 template <typename TIn, int PAD>
@@ -61,7 +61,9 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
   const int b = bf / a.F, f = bf - b * a.F;
   const long long row = a.f_major ? ((long long)f * a.B + b) : (long long)bf;
   const int row_elems = NC ? (a.pairs ? ((a.N + 1) / 2) * 8 : a.N * a.cp) : a.C * a.N;
-  TOut* out_row = reinterpret_cast<TOut*>(a.out) + (a.pairs ? row * 8 : row * row_elems);
+  // pair layout: rows are tiled by 128; this row's 16-byte slot of pair p sits at ((tile*n_pairs + p)*128 + r)*8
+  TOut* out_row = reinterpret_cast<TOut*>(a.out) +
+                  (a.pairs ? ((row >> 7) * (long long)((a.N + 1) / 2) * 128 + (row & 127)) * 8 : row * row_elems);
   TOut* dst = STAGE ? stage : out_row;
 
   const float fr = __ldg(a.fix_rc + 2 * bf), fc = __ldg(a.fix_rc + 2 * bf + 1);
@@ -124,9 +126,9 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
   }
 
   if (STAGE && NC && a.pairs) {
-    // pair layout: this row owns one 16-byte slot in every pair's block of B*F rows
+    // pair layout: this row owns one 16-byte slot in each pair's 128-row block of its row tile
     __syncthreads();
-    const long long rows = (long long)a.B * a.F;
+    const long long rows = 128;
     const int4* s4 = reinterpret_cast<const int4*>(stage);
     int4* d4 = reinterpret_cast<int4*>(out_row);
     const int n_pairs = (a.N + 1) / 2;

@@ -59,7 +59,8 @@ class SamplerPlan:
 def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=None, layout=OUT_BFCN, channel_stride=None, out=None):
     """img [B,C,H,W] (any strides); fix_rc, fix_hw [B,F,2] float32 CUDA.  Returns the sampled
     tensor in `layout`: [B,F,C,N], [F,B,C,N], [B,F,N,Cp], [F,B,N,Cp], or the pair layout
-    [ceil(N/2), F*B (or B*F) rows, 8] that a KNNConv plan with c_in <= 4 consumes."""
+    [ceil(rows/128), ceil(N/2), 128, 8] (rows = F*B or B*F) that a KNNConv plan with c_in <= 4
+    consumes; rows past the last one are left unwritten."""
     _need_cuda(img, fix_rc, fix_hw)
     B, Cc, H, W = img.shape
     fix_rc = fix_rc.to(torch.float32).contiguous()
@@ -73,7 +74,7 @@ def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=No
     lead = (F, B) if layout in (OUT_FBCN, OUT_FBNC) else (B, F)
     if pairs:
         out_dtype, cp = torch.bfloat16, 8
-        shape = ((plan.n_points + 1) // 2, B * F, 8)
+        shape = ((B * F + 127) // 128, (plan.n_points + 1) // 2, 128, 8)
     else:
         shape = lead + ((plan.n_points, cp) if nc else (Cc, plan.n_points))
     if out is None:
@@ -132,14 +133,14 @@ class KnnConvPlan:
             check(lib.fovi_knnconv_pack_weights(self._h, _ptr(weight), _dt(weight.dtype), _ptr(dst), _dt(dtype), _stream()), "fovi_knnconv_pack_weights")
         return dst
 
-    def forward(self, x_bnc, wt, bias=None, relu=False, out_dtype=torch.bfloat16, out=None):
+    def forward(self, x_bnc, wt, bias=None, relu=False, out_dtype=torch.bfloat16, out=None, batch=None):
         """Tensor-core path.  x_bnc: bf16 contiguous, [B,n_in,cin_packed] or (pair layout)
-        [n_pairs,B,8]  ->  [B,n_out,c_out]."""
+        [ceil(B/128),n_pairs,128,8] with `batch` = B  ->  [B,n_out,c_out]."""
         _need_cuda(x_bnc, wt, bias)
         assert x_bnc.dtype == torch.bfloat16 and x_bnc.is_contiguous() and wt.dtype == torch.bfloat16 and wt.is_contiguous()
         if self.x_layout == X_PAIRS:
-            B = x_bnc.shape[1]
-            assert x_bnc.shape == (self.n_pairs, B, 8), x_bnc.shape
+            B = x_bnc.shape[0] * 128 if batch is None else int(batch)
+            assert x_bnc.shape == ((B + 127) // 128, self.n_pairs, 128, 8), (x_bnc.shape, B)
             assert wt.dim() == 4 and wt.shape[0] == self.n_out and wt.shape[2:] == (self.c_out, 8), wt.shape
         else:
             B = x_bnc.shape[0]
@@ -178,14 +179,15 @@ class KnnConvPlan:
 
 def pack_points(x, cp=8, x_layout=X_BNC):
     """x [B,C,N] float32/bf16 -> tensor-core input: [B,N,cp] bf16 (pad channels zero) or the pair
-    layout [ceil(N/2),B,8].  Pass a KnnConvPlan as `cp` to get the layout that plan consumes."""
+    layout [ceil(B/128),ceil(N/2),128,8].  Pass a KnnConvPlan as `cp` to get the layout that plan consumes."""
     _need_cuda(x)
     if isinstance(cp, KnnConvPlan):
         cp, x_layout = cp.cin_packed, cp.x_layout
     x = x.contiguous()
     B, Cc, N = x.shape
-    shape = ((N + 1) // 2, B, 8) if x_layout == X_PAIRS else (B, N, cp)
-    dst = torch.empty(shape, dtype=torch.bfloat16, device=x.device)
+    shape = ((B + 127) // 128, (N + 1) // 2, 128, 8) if x_layout == X_PAIRS else (B, N, cp)
+    # the pad rows of the last 128-row tile are zeroed so that the buffer holds no stray bit patterns
+    dst = (torch.zeros if x_layout == X_PAIRS else torch.empty)(shape, dtype=torch.bfloat16, device=x.device)
     with torch.cuda.device(x.device):
         check(lib.fovi_pack_points(_ptr(x), _dt(x.dtype), B, Cc, N, _ptr(dst), cp, x_layout, _stream()), "fovi_pack_points")
     return dst

@@ -44,18 +44,21 @@ typedef enum {
   FOVI_OUT_BFNC = 2, /* [B,F,N,Cp] points-major, channels last, Cp = out_channel_stride >= C,
                         channels C..Cp-1 written as 0: the KNNConv kernels' input layout      */
   FOVI_OUT_FBNC = 3, /* [F,B,N,Cp]                                                            */
-  FOVI_OUT_FB_PAIRS = 4, /* [ceil(N/2), F*B, 2, 4]: point pairs outermost, then the image x fixation
-                            row (f*B + b), then the two points of the pair with 4 channels each
-                            (channels C..3 and an odd last point written as 0); bf16, C <= 4.
-                            The input layout of a KNNConv plan with c_in <= 4 (FOVI_X_PAIRS).  */
+  FOVI_OUT_FB_PAIRS = 4, /* [ceil(F*B/128), ceil(N/2), 128, 2, 4]: tiles of 128 image x fixation rows
+                            (row = f*B + b) outermost, then point pairs, then the rows of the tile,
+                            then the two points of the pair with 4 channels each (channels C..3 and
+                            an odd last point are written as 0; rows past F*B are not written);
+                            bf16, C <= 4.  The input layout of a KNNConv plan with c_in <= 4
+                            (FOVI_X_PAIRS).                                                     */
   FOVI_OUT_BF_PAIRS = 5  /* same with row = b*F + f                                            */
 } fovi_sample_layout;
 
 /* Input layout the tensor-core path of a KNNConv plan expects (fovi_knnconv_x_layout). */
 typedef enum {
   FOVI_X_BNC = 0,  /* [B, n_in, cin_packed] bf16, channels last                                */
-  FOVI_X_PAIRS = 1 /* [ceil(n_in/2), B, 2, 4] bf16 (see FOVI_OUT_FB_PAIRS); chosen when c_in <= 4:
-                      a neighbour pair of all 128 batch rows is one contiguous 2 KB block        */
+  FOVI_X_PAIRS = 1 /* [ceil(B/128), ceil(n_in/2), 128, 2, 4] bf16 (see FOVI_OUT_FB_PAIRS); chosen when
+                      c_in <= 4: a run of consecutive point pairs of one 128-row batch tile is one
+                      contiguous block of 2 KB per pair; values must be finite                  */
 } fovi_x_layout;
 
 /* Activation layouts of KNNConv. */
@@ -144,7 +147,7 @@ int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* plan, int dst_
 
 /* Convert activations [B,C,N] (x_dtype, contiguous) to a tensor-core input layout:
  * x_layout FOVI_X_BNC: [B,N,cp] bf16 with zero-filled pad channels (cp >= C, multiple of 8);
- * x_layout FOVI_X_PAIRS: [ceil(N/2),B,2,4] bf16 (C <= 4; cp ignored). */
+ * x_layout FOVI_X_PAIRS: [ceil(B/128),ceil(N/2),128,2,4] bf16 (C <= 4; cp ignored). */
 int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, int x_layout, void* stream);
 
 /* Tensor-core path (tcgen05 MMA, bf16 operands, fp32 accumulation in tensor memory).

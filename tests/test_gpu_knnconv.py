@@ -38,7 +38,7 @@ def bf16_round(a):
 def run_tc(ops, plan, x_bcn, w, bias=None, relu=False, out_dtype=torch.float32):
     wt = plan.pack_weights(dev(w))
     xp = ops.pack_points(dev(x_bcn), plan)
-    y = plan.forward(xp, wt, None if bias is None else dev(bias), relu=relu, out_dtype=out_dtype)
+    y = plan.forward(xp, wt, None if bias is None else dev(bias), relu=relu, out_dtype=out_dtype, batch=x_bcn.shape[0])
     plan.check()
     return y.to(torch.float32).permute(0, 2, 1).cpu().numpy()
 
@@ -87,7 +87,7 @@ def test_config3_stack_tensor_core(ops, golden):
         if h is None:
             h = ops.pack_points(dev(x), plan)
         wt = plan.pack_weights(dev(w))
-        h = plan.forward(h, wt, torch.zeros(chans[i + 1], device="cuda"), relu=i < 4, out_dtype=torch.bfloat16)
+        h = plan.forward(h, wt, torch.zeros(chans[i + 1], device="cuda"), relu=i < 4, out_dtype=torch.bfloat16, batch=2)
         plan.check()
         got = h.to(torch.float32).permute(0, 2, 1).cpu().numpy()
         e = rel_l2(got, acts[f"act{i}"])
@@ -164,5 +164,5 @@ def test_empty_batch(ops, golden):
     g = golden("config4_patch_embed_p8.npz")
     plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), int(g["V"]), 3, 384)
     wt = plan.pack_weights(torch.zeros((384, 3 * int(g["V"])), device="cuda"))
-    y = plan.forward(torch.empty((plan.n_pairs, 0, 8), dtype=torch.bfloat16, device="cuda"), wt)
+    y = plan.forward(torch.empty((0, plan.n_pairs, 128, 8), dtype=torch.bfloat16, device="cuda"), wt, batch=0)
     assert y.shape == (0, plan.n_out, 384)

@@ -71,13 +71,13 @@ def test_layouts_and_strided_input(ops, golden):
     y = ops.sample(plan, xd, dev(fix), dev(hw), layout=ops.OUT_FBNC, channel_stride=4)
     got = y.cpu().numpy()
     assert np.array_equal(got[..., :3], ref.transpose(1, 0, 3, 2)) and np.all(got[..., 3:] == 0)
-    # pair layout consumed by the first KNNConv: [ceil(N/2), rows, 2 points x 4 channels] bf16
+    # pair layout consumed by the first KNNConv: [row tiles of 128, ceil(N/2), 128, 2 points x 4 channels] bf16
     ref16 = torch.from_numpy(ref).to(torch.bfloat16).to(torch.float32).numpy()
     N = ref.shape[-1]
     for layout, rows_ref in ((ops.OUT_FB_PAIRS, ref16.transpose(1, 0, 2, 3)), (ops.OUT_BF_PAIRS, ref16)):
         y = ops.sample(plan, xd, dev(fix), dev(hw), layout=layout)
-        assert y.shape == ((N + 1) // 2, B * F, 8) and y.dtype == torch.bfloat16
-        got = y.to(torch.float32).cpu().numpy().reshape((N + 1) // 2, B * F, 2, 4)
+        assert y.shape == (1, (N + 1) // 2, 128, 8) and y.dtype == torch.bfloat16
+        got = y.to(torch.float32).cpu().numpy()[0, :, :B * F].reshape((N + 1) // 2, B * F, 2, 4)
         want = np.zeros(((N + 1) // 2 * 2, B * F, 4), f32)
         want[:N, :, :3] = rows_ref.reshape(B * F, 3, N).transpose(2, 0, 1)
         assert np.array_equal(got.transpose(0, 2, 1, 3).reshape(-1, B * F, 4), want)
