@@ -28,8 +28,8 @@
 //          [point pair][batch row][2 points x 4 channels], so the 128 batch rows of one pair are
 //          ONE contiguous 2 KB block that already is the un-swizzled core-matrix layout, and the
 //          weights are pre-gathered per output point and c_out tile so the eight slabs of a stage
-//          are one contiguous block too.  Both move with plain bulk copies (cp.async.bulk): TMA
-//          handles a box of 16-byte rows one row at a time, a contiguous block at full width.
+//          are one contiguous block too.  Both move with plain bulk copies (cp.async.bulk), one
+//          per lane of the producer warp, so the nine copies of a stage issue as one instruction.
 //          One MMA (K=16) consumes two pairs = four neighbours.  Unused slots read a block of
 //          zeros; rows past the batch keep stale shared memory, which only reaches output rows
 //          that are never stored.
@@ -120,6 +120,16 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -230,8 +240,33 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       }
       const int* tb_idx = reinterpret_cast<const int*>(tbl0 + buf * tbl_pitch);
       const uint16_t* tb_tap = reinterpret_cast<const uint16_t*>(tbl0 + buf * tbl_pitch + (size_t)a.kp * 4);
-      if (lane == 0) {
-        const int m0 = mt * BM, o0 = ctile * a.ct;
+      const int m0 = mt * BM, o0 = ctile * a.ct;
+      if (MODE == MODE_PAIRS) {
+        // The whole warp issues: lane j < 8 copies the 2 KB block of slot j, lane 8 the eight weight slabs.
+        // (A single thread pays the full issue cost of every copy in sequence; nine lanes pay it once.)
+        const int steps = (cnt + 7) / 8;
+        const uint32_t b_bytes = 8u * (uint32_t)a.ct * 16u;
+        const unsigned char* wn = a.Wt + ((size_t)n * a.n_ct + ctile) * a.kp * ((size_t)a.ct * 16);
+        const unsigned char* xt = a.X + (size_t)mt * a.n_pairs * 2048;  // this batch tile's pair blocks
+        for (int st = 0; st < steps; ++st) {
+          const uint32_t full = smem_u32(&hdr->full[s]);
+          if (lane == 0) {
+            ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1);
+            if (ok) mbar_expect_tx(full, a.stage_bytes);
+          }
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          const uint32_t sa = stages0 + s * a.stage_bytes;
+          if (lane < 8) {
+            const int pr = tb_idx[st * 8 + lane];  // unused tail slots hold n_pairs: they read zeros
+            bulk_load(sa + lane * 2048u, pr < a.n_pairs ? xt + (size_t)pr * 2048 : a.zero_block, 2048u, full);
+          } else if (lane == 8) {
+            bulk_load(sa + b_stage_off, wn + (size_t)st * b_bytes, b_bytes, full);
+          }
+          ++issued;
+          if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+        }
+      } else if (lane == 0) {
         if (C64) {
           const int steps = cnt * chunks;
           int k = 0, cc = 0;
@@ -244,33 +279,6 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             tma_load_3d(sa + b_stage_off, &tmB, full, cc * 64, o0, tb_tap[k]);
             ++issued;
             if (++cc == chunks) { cc = 0; ++k; }
-            if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
-          }
-        } else if (MODE == MODE_PAIRS) {
-          const int steps = (cnt + 7) / 8;
-          const uint32_t b_bytes = 8u * (uint32_t)a.ct * 16u;
-          const unsigned char* wn = a.Wt + ((size_t)n * a.n_ct + ctile) * a.kp * ((size_t)a.ct * 16);
-          const unsigned char* xt = a.X + (size_t)mt * a.n_pairs * 2048;  // this batch tile's pair blocks
-          for (int st = 0; st < steps; ++st) {
-            const uint32_t full = smem_u32(&hdr->full[s]);
-            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
-            mbar_expect_tx(full, a.stage_bytes);
-            const uint32_t sa = stages0 + s * a.stage_bytes;
-            const int* sl = tb_idx + st * 8;
-            int j = 0;
-            while (j < 8) {  // the slots are sorted by pair index: copy each run of consecutive pairs at once
-              const int pr = sl[j];
-              if (pr >= a.n_pairs) {  // unused tail slots
-                bulk_load(sa + j * 2048u, a.zero_block, (uint32_t)(8 - j) * 2048u, full);
-                break;
-              }
-              int len = 1;
-              while (j + len < 8 && sl[j + len] == pr + len && pr + len < a.n_pairs) ++len;
-              bulk_load(sa + j * 2048u, xt + (size_t)pr * 2048, (uint32_t)len * 2048u, full);
-              j += len;
-            }
-            bulk_load(sa + b_stage_off, wn + (size_t)st * b_bytes, b_bytes, full);  // eight pre-gathered slabs
-            ++issued;
             if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
           }
         } else {
@@ -293,6 +301,9 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
           }
         }
+      }
+      if (MODE != MODE_PAIRS) {  // lane 0 carried the ring position and the outcome
+        s = __shfl_sync(0xffffffffu, s, 0); ph = __shfl_sync(0xffffffffu, ph, 0); issued = __shfl_sync(0xffffffffu, issued, 0);
       }
       __syncwarp();
       if (next < a.total_items) {  // park the prefetched list in the other buffer
@@ -381,31 +392,40 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const int o0 = ctile * a.ct;
       const size_t y_off = ((size_t)row * a.n_out + n) * a.c_out + o0;
       const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + acc * 256u;
-      for (int c0 = 0; c0 < a.ct; c0 += 16) {
-        uint32_t r[16];
-        tc_ld16(t_base + c0, r);
+      // 64 accumulator columns per round: two 32-column tensor-memory loads in flight, one wait
+      for (int c0 = 0; c0 < a.ct; c0 += 64) {
+        uint32_t r[64];
+        const int w = min(64, a.ct - c0);  // 16, 32, 48 or 64 (ct is a multiple of 16)
+        if (w >= 32) tc_ld32(t_base + c0, r); else tc_ld16(t_base + c0, *reinterpret_cast<uint32_t(*)[16]>(r));
+        if (w == 64) tc_ld32(t_base + c0 + 32, r + 32);
+        else if (w == 48) tc_ld16(t_base + c0 + 32, *reinterpret_cast<uint32_t(*)[16]>(r + 32));
         tc_ld_wait();
-        float v[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float x = (cnt > 0 ? __uint_as_float(r[i]) : 0.f) + bias_s[o0 + c0 + i];
-          v[i] = a.relu ? fmaxf(x, 0.f) : x;
-        }
-        if (row < a.B) {
-          if (a.y_f32) {
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.Y) + y_off + c0);
+        for (int g = 0; g < 4; ++g) {  // groups of 16 columns
+          if (g * 16 < w) {
+            float v[16];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          } else {
-            uint32_t pk[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-              pk[i] = *reinterpret_cast<uint32_t*>(&h);
+            for (int i = 0; i < 16; ++i) {
+              const float x = (cnt > 0 ? __uint_as_float(r[g * 16 + i]) : 0.f) + bias_s[o0 + c0 + g * 16 + i];
+              v[i] = a.relu ? fmaxf(x, 0.f) : x;
             }
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + y_off + c0);
-            dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            if (row < a.B) {
+              if (a.y_f32) {
+                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              } else {
+                uint32_t pk[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                  pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + y_off + c0 + g * 16);
+                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+              }
+            }
           }
         }
       }
