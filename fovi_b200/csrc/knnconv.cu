@@ -305,3 +305,69 @@ extern "C" int fovi_knnconv_forward_f32(const fovi_knnconv_plan* p, const void* 
 #undef RUN
   return fovi::after_launch("knnconv_f32_kernel");
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free forward from the reference's [B, c_in, n_in] layout.
+//
+// Some hosts may not allocate device memory at the point where they run a layer: code inside a
+// real-time loop or a serving thread that was handed a fixed memory budget at start-up, or a
+// plug-in whose host application owns the allocator and forbids allocation calls from callbacks
+// (cudaMalloc also synchronises the whole device, which such hosts cannot afford).  For them the
+// repacked copy of the activations that the tensor-core kernel reads lives in the fixed array
+// below instead of a caller-provided or freshly allocated buffer.
+//
+// The array is part of the library image: every GPU that loads the library holds these bytes
+// until the process exits.  All calls on a device share it and it keeps the last call's contents,
+// so two calls that overlap on the GPU (different streams) race; issue them on one stream.
+#define FOVI_STATIC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[FOVI_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_static_scratch on each device.  In host code the array's name is only a
+// handle for the runtime, not an address a kernel could use, so it is resolved once per device.
+int static_scratch_address(unsigned char** out) {
+  static unsigned char* addr[64] = {nullptr};
+  int dev = -1;
+  FOVI_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return FOVI_ERR_UNSUPPORTED;
+  if (!addr[dev]) {
+    void* p = nullptr;
+    FOVI_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));  // the current device is `dev`
+    addr[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = addr[dev];
+  return FOVI_OK;
+}
+}  // namespace
+
+extern "C" int64_t fovi_static_scratch_bytes(void) { return (int64_t)FOVI_STATIC_SCRATCH_BYTES; }
+
+extern "C" int fovi_knnconv_forward_bcn_static(fovi_knnconv_plan* p, const void* X, int x_dtype, const void* Wt,
+                                               const float* bias, void* Y, int y_dtype, int B, int relu, void* stream) {
+  if (!p || !fovi::valid_dtype(x_dtype) || !fovi::valid_dtype(y_dtype) || B < 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;
+  if (!X || !Wt || !Y) return FOVI_ERR_INVALID_ARGUMENT;
+  const bool pairs = p->x_layout == FOVI_X_PAIRS;
+  const long long need = pairs ? (long long)((B + 127) / 128) * p->n_pairs * 2048
+                               : (long long)B * p->n_in * p->cin_packed * 2;
+  if (need > (long long)FOVI_STATIC_SCRATCH_BYTES) {
+    fovi::g_last_cuda_error = "fovi_knnconv_forward_bcn_static: the packed activations need " + std::to_string(need) +
+                              " bytes, the static scratch holds " + std::to_string(FOVI_STATIC_SCRATCH_BYTES) +
+                              "; use a smaller batch or fovi_pack_points + fovi_knnconv_forward";
+    return FOVI_ERR_UNSUPPORTED;
+  }
+  unsigned char* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (pairs && (B & 127)) {
+    // The pad rows of the last 128-row tile are never written by the repack: clear them, so that no
+    // bit pattern left by an earlier call is fed to the tensor cores.
+    const int r0 = B & 127;
+    unsigned char* tile = scratch + (size_t)(B / 128) * p->n_pairs * 2048;
+    FOVI_CUDA(cudaMemset2DAsync(tile + (size_t)r0 * 16, 2048, 0, (size_t)(128 - r0) * 16, p->n_pairs, st));
+  }
+  rc = fovi_pack_points(X, x_dtype, B, p->c_in, p->n_in, scratch, p->cin_packed, p->x_layout, stream);
+  if (rc) return rc;
+  return fovi_knnconv_forward(p, scratch, Wt, bias, Y, y_dtype, B, relu, stream);
+}

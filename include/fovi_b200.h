@@ -161,6 +161,25 @@ int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst,
 int fovi_knnconv_forward(fovi_knnconv_plan* plan, const void* X, const void* Wt, const float* bias, void* Y,
                          int y_dtype, int B, int relu, void* stream);
 
+/* Allocation-free variant of the tensor-core path for inputs in the reference's [B,c_in,n_in]
+ * layout.  It has no counterpart in the reference (which leaves all memory to PyTorch's caching
+ * allocator); it exists for callers that must not allocate device memory where they run the
+ * layer — a real-time or serving loop with a budget fixed at start-up, a plug-in callback under a
+ * host that owns the allocator — and for whom cudaMalloc's device-wide synchronisation is not
+ * acceptable either.  The repacked activations are kept in a fixed array inside the library
+ * (fovi_static_scratch_bytes(), 32 MiB, resident on every GPU that loads the library until exit)
+ * instead of a buffer the caller would have to provide.  Larger batches are rejected with
+ * FOVI_ERR_UNSUPPORTED and a message in fovi_last_cuda_error().  No cudaMalloc/cudaFree or other
+ * allocating call is made.  The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture.  All calls on a device
+ * share the array and it keeps the previous call's contents (the parts that must be zero are
+ * cleared on every call): calls that overlap on the GPU race, so issue them on one stream.
+ * X: [B,c_in,n_in] of x_dtype (f32 or bf16), contiguous; the other arguments as for
+ * fovi_knnconv_forward. */
+int64_t fovi_static_scratch_bytes(void);
+int fovi_knnconv_forward_bcn_static(fovi_knnconv_plan* plan, const void* X, int x_dtype, const void* Wt,
+                                    const float* bias, void* Y, int y_dtype, int B, int relu, void* stream);
+
 /* Exact float32 path (CUDA cores, float32 multiply-adds): the fp32 parity case.
  * X : [B,c_in,n_in] (FOVI_ACT_BCN) or [B,n_in,c_in] (FOVI_ACT_BNC) of x_dtype; Wt: packed
  * f32 slabs [V,c_out,cin_packed]; Y: float32 in y_layout. */
