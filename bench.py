@@ -30,20 +30,26 @@ METRIC = "images x fixations/s through sensor+KNNConv"
 UNIT = "img*fix/s"
 
 
-def load_tables():
-    t = dict(np.load(os.path.join(ROOT, "tests", "golden", "config3_tables.npz")))
-    s = dict(np.load(os.path.join(ROOT, "tests", "golden", "sensor_a1.npz")))
-    return s, t
+FOV, CMF_A, STRIDES, KS = 16, 1.0, [2, 2, 1, 1, 1], [121, 25, 9, 9, 9]
 
 
-def make_weights():
-    rs = np.random.RandomState(1)
-    s, t = load_tables()
-    ws = []
+def layer_geometry():
+    """Point sets and (K, reference-frame side) of the five layers, built by the package's host geometry
+    exactly as fovi's KNNAlexNet chains them (auto-matched to a 64x64 cartesian budget)."""
+    from fovi_b200.coords import auto_match_num_coords, get_in_out_coords
+    in_res, cart_res = auto_match_num_coords(FOV, CMF_A, 64, "isotropic", 1)
+    out = []
     for i in range(5):
-        V = int(t[f"l{i}_V"])
-        ws.append((rs.standard_normal((CHANS[i + 1], CHANS[i] * V)) * np.sqrt(2.0 / (CHANS[i] * V))).astype(np.float32))
-    return ws
+        ic, oc, out_cart = get_in_out_coords(in_res, FOV, CMF_A, STRIDES[i], auto_match_cart_resources=1, in_cart_res=cart_res)
+        out.append((ic, oc, KS[i], int(np.ceil(2 * np.sqrt(KS[i])))))
+        in_res, cart_res = oc.resolution, out_cart
+    return out
+
+
+def make_weights(geo):
+    rs = np.random.RandomState(1)
+    return [(rs.standard_normal((CHANS[i + 1], CHANS[i] * side * side)) * np.sqrt(2.0 / (CHANS[i] * side * side))).astype(np.float32)
+            for i, (_, _, _, side) in enumerate(geo)]
 
 
 def workload_name(args):
@@ -97,52 +103,87 @@ class ClockSampler:
                 "reasons": sorted(v for k, v in self.REASONS.items() if self.mask & k)}
 
 
-def cpu_baseline(n_images, n_fix, threads):
-    """The oracle (a NumPy port of the reference's CPU path) timed on a bounded sample of the workload."""
-    from oracle import fovi_oracle as oracle
-    s, t = load_tables()
-    ws = make_weights()
-    rs = np.random.RandomState(0)
-    x = rs.random_sample((n_images, 3, 256, 256)).astype(np.float32)
-    fix = (0.25 + 0.5 * rs.random_sample((n_images, n_fix, 2))).astype(np.float32)
-    hw = np.full((n_images, n_fix, 2), 256, np.float32)
+class CpuPath:
+    """The oracle — a port of the reference's CPU path for this workload (C with POSIX threads when it builds,
+    else NumPy) — with tables and weights set up once; `run(n_images)` does one pass on a bounded sample."""
 
-    def run():
-        y = oracle.retinal_sample(x, s["sampling_grid"], fix, hw)                       # [B,F,3,N]
-        h = y.transpose(1, 0, 2, 3).reshape(n_images * n_fix, 3, -1)                     # (f b) c n
+    def __init__(self, n_fix):
+        from fovi_b200 import tables
+        from oracle import fovi_oracle
+        self.np_oracle = fovi_oracle
+        try:
+            from oracle import c_oracle
+            c_oracle.load()
+            self.c, self.kind, self.cores = c_oracle, "C/pthreads", c_oracle.threads()
+        except Exception:
+            self.c, self.kind, self.cores = None, "NumPy", os.cpu_count()
+        geo = layer_geometry()
+        self.ws = make_weights(geo)
+        self.tabs = []
+        for ic, oc, k, side in geo:
+            idx, _, pts, cart = tables.knn_table(ic, oc, k)
+            ref, _ = tables.reference_frame(k, side)
+            tap, _ = tables.tap_table(idx, pts, cart, oc, ref)
+            self.tabs.append((tables.pad_token_table(idx, len(ic)).numpy().astype(np.int32), tap.numpy().astype(np.int64), side * side))
+        c0 = geo[0][0].cartesian
+        self.grid = np.stack([c0[:, 0].numpy(), -c0[:, 1].numpy()], 1)
+        self.n_fix = n_fix
+
+    def run(self, n_images, seed=0):
+        rs = np.random.RandomState(seed)
+        x = rs.random_sample((n_images, 3, 256, 256)).astype(np.float32)
+        fix = (0.25 + 0.5 * rs.random_sample((n_images, self.n_fix, 2))).astype(np.float32)
+        hw = np.full((n_images, self.n_fix, 2), 256, np.float32)
+        t0 = time.perf_counter()
+        impl = self.c if self.c is not None else self.np_oracle
+        y = impl.retinal_sample(x, self.grid, fix, hw)                                              # [B,F,3,N]
+        h = np.ascontiguousarray(y.transpose(1, 0, 2, 3).reshape(n_images * self.n_fix, 3, -1))     # (f b) c n
         for i in range(5):
-            h = oracle.knnconv_forward(h, t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"].astype(np.int64), int(t[f"l{i}_V"]), ws[i], np.zeros(CHANS[i + 1], np.float32))
-            if i < 4:
-                h = np.maximum(h, 0)
-        return h
-    run()
-    t0 = time.perf_counter(); reps = 0
-    while reps < 2 or time.perf_counter() - t0 < 8.0:
-        run(); reps += 1
-    dt = (time.perf_counter() - t0) / reps
-    return n_images * n_fix / dt, dt
+            idx, tap, V = self.tabs[i]
+            zero = np.zeros(CHANS[i + 1], np.float32)
+            if self.c is not None:
+                h = self.c.knnconv_forward_closed_form(h, idx, tap, V, self.ws[i], zero, relu=i < 4)
+            else:
+                h = self.np_oracle.knnconv_forward(h, idx, tap, V, self.ws[i], zero)
+                h = np.maximum(h, 0) if i < 4 else h
+        return time.perf_counter() - t0
+
+    def sample_text(self, n_images):
+        return (f"{n_images} images x {self.n_fix} fixations per pass (same sensor, tables and weights), float32, "
+                f"{self.kind} port of the reference path on {self.cores} threads")
+
+
+def cpu_baseline(n_fix, budget_s=10.0):
+    """Times the CPU port for about `budget_s` seconds.  Returns the cpu_baseline object of the JSON line."""
+    path = CpuPath(n_fix)
+    n_images = 8
+    path.run(n_images)                                   # warm-up (page faults, thread start)
+    t0 = time.perf_counter(); times = []
+    while len(times) < 3 or time.perf_counter() - t0 < budget_s:
+        times.append(path.run(n_images))
+    v = n_images * n_fix / float(np.median(times))
+    return {"value": v, "unit": UNIT, "cores": path.cores, "kind": "port", "sample": path.sample_text(n_images)}
 
 
 def run_reference(args):
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """`--impl reference`: the reference's own implementation is Python + PyTorch and cannot travel to the GPU
+    box, and it has nothing to compile (no oracle/_ref), so this arm times the oracle port of its CPU path on all
+    host threads.  A step = one pass over a bounded sample of the workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    threads = os.cpu_count()
-    n_img, n_fix = 2, args.fixations
-    vals = []
-    for _ in range(args.warmup):
-        cpu_baseline(n_img, n_fix, threads)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        v, dt = cpu_baseline(n_img, n_fix, threads)
-        vals.append(v)
-    v = float(np.median(vals))
-    sample = f"{n_img} images x {n_fix} fixations per step (same sensor, tables and weights), float32"
+    path = CpuPath(args.fixations)
+    n_images = 8
+    for _ in range(max(args.warmup, 1)):
+        path.run(n_images)
+    times = [path.run(n_images, seed=s) for s in range(args.steps)]
+    per_step = float(np.sum(times)) / args.steps
+    v = n_images * args.fixations / per_step
+    sample = path.sample_text(n_images)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 * n_img * n_fix / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "ms_per_step": 1e3 * per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": workload_name(args), "sample": sample},
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": path.cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -150,11 +191,12 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--fixations", type=int, default=4)
+    ap.add_argument("--chunks", type=int, default=8, help="chunks of the host->device->host pipeline (e2e)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -163,6 +205,9 @@ def main():
     import torch
     import torch.distributed as dist
     from fovi_b200 import ops
+    from fovi_b200.knn import KNNConvLayer, KNNConvStack
+    from fovi_b200.pipeline import FoveatedFrontEnd
+    from fovi_b200.sensing import RetinalTransform
 
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -170,77 +215,75 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    warmup = max(args.warmup, 3)
 
-    s, t = load_tables()
-    ws = make_weights()
+    # ---- the model of the workload, through the public module API
+    geo = layer_geometry()
+    ws = make_weights(geo)
+    retina = RetinalTransform(resolution=64, start_res=256, fov=FOV, cmf_a=CMF_A, sampler="grid_bilinear", fixation_size=256, device=dev)
+    layers = []
+    for i, (ic, oc, k, side) in enumerate(geo):
+        L = KNNConvLayer(CHANS[i], CHANS[i + 1], k, ic, oc, device=dev, ref_frame_side_length=side, bias=True)
+        L.weight.data.copy_(torch.from_numpy(ws[i]))
+        layers.append(L)
+    front = FoveatedFrontEnd(retina, KNNConvStack(layers))
+    plans = [L.plan for L in layers]
+
     B, F = args.batch, args.fixations
     M = B * F
-    splan = ops.SamplerPlan(s["sampling_grid"], dev)
-    plans, wts, biases = [], [], []
-    for i in range(5):
-        p = ops.KnnConvPlan(t[f"l{i}_knn_idx_pad"], t[f"l{i}_tap"], int(t[f"l{i}_n_in"]), int(t[f"l{i}_V"]), CHANS[i], CHANS[i + 1], dev)
-        plans.append(p); wts.append(p.pack_weights(torch.from_numpy(ws[i]).to(dev))); biases.append(torch.zeros(CHANS[i + 1], device=dev))
     rs = np.random.RandomState(1000 + rank)
     x_host = torch.from_numpy(rs.random_sample((B, 3, 256, 256)).astype(np.float32)).pin_memory()
     fix_host = torch.from_numpy((0.25 + 0.5 * rs.random_sample((B, F, 2))).astype(np.float32)).pin_memory()
-    hw = torch.full((B, F, 2), 256.0, device=dev)
-    x_dev = x_host.to(dev); fix_dev = fix_host.to(dev)
-    # preallocated activations (channels-last points layout), reused every step
-    acts = [torch.zeros(((M + 127) // 128, (splan.n_points + 1) // 2, 128, 8), dtype=torch.bfloat16, device=dev)]   # pair layout
-    for i in range(5):
-        acts.append(torch.empty((M, plans[i].n_out, CHANS[i + 1]), dtype=torch.bfloat16, device=dev))
-    out_host = torch.empty(acts[-1].shape, dtype=torch.bfloat16).pin_memory()
+    x_dev, fix_dev = x_host.to(dev), fix_host.to(dev)
+    out_host = torch.empty((F, B, plans[-1].n_out, CHANS[-1]), dtype=torch.bfloat16).pin_memory()
     flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
     kernel_events = []
 
-    def step(x, fix, record=None):
-        marks = [ev() for _ in range(7)] if record is not None else None
-        if marks: marks[0].record()
-        ops.sample(splan, x, fix, hw, layout=ops.OUT_FB_PAIRS, out=acts[0])
-        if marks: marks[1].record()
-        for i in range(5):
-            plans[i].forward(acts[i], wts[i], biases[i], relu=i < 4, out=acts[i + 1], batch=M)
-            if marks: marks[i + 2].record()
-        if marks: record.append(marks)
-        return acts[-1]
+    def device_step(record):
+        if record is None:
+            return front.forward(x_dev, fix_dev)
+        marks = [ev() for _ in range(7)]
+        marks[0].record()
+        y = front.forward(x_dev, fix_dev, between=lambda i: marks[i + 1].record())
+        record.append(marks)
+        return y
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup, record=None):
-        for _ in range(warmup):
+    def timed(fn, steps, n_warm, record=None):
+        for _ in range(n_warm):
             flush.zero_(); fn(None)
         barrier()
-        t = 0.0
-        l0 = ops.launch_count()
+        t, l0 = 0.0, ops.launch_count()
         for _ in range(steps):
-            flush.zero_()                       # L2 flush between timed iterations (excluded from the time)
+            flush.zero_()                       # L2 flush between timed iterations (outside the timed events)
             a, b = ev(), ev()
             a.record(); fn(record); b.record()
             b.synchronize()
             t += a.elapsed_time(b)
+        launches = ops.launch_count() - l0
         barrier()
         tt = torch.tensor([t], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        return float(tt.item()), ops.launch_count() - l0
+        return float(tt.item()), launches
 
     clocks = ClockSampler(local)
     clocks.start()
-    ms_total, launches = timed(lambda rec: step(x_dev, fix_dev, rec), args.steps, max(args.warmup, 3), kernel_events)
-
-    def e2e_step(_):
-        xd = x_host.to(dev, non_blocking=True); fd = fix_host.to(dev, non_blocking=True)
-        y = step(xd, fd)
-        out_host.copy_(y, non_blocking=True)
+    ms_total, launches = timed(device_step, args.steps, warmup, kernel_events)
     clk = clocks.stop()
-    ms_e2e, _ = timed(e2e_step, args.steps, 3)
+    ms_e2e, _ = timed(lambda _r: front.run_from_host(x_host, fix_host, out_host, chunks=args.chunks), args.steps, 3)
     for p in plans:
         p.check()
+    # the pipelined host path and the device path compute the same thing
+    y_dev = front.forward(x_dev, fix_dev).view(F, B, plans[-1].n_out, CHANS[-1])
+    torch.cuda.synchronize()
+    e2e_matches = bool(torch.equal(y_dev.cpu(), out_host))
 
     # per-kernel times from the events recorded inside the timed steps
     per = np.zeros(6)
@@ -253,41 +296,40 @@ def main():
     pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(pk):
         d = json.load(open(pk))
-        # the conv launches are 0.15-0.5 ms bursts inside a ~1.5 ms step: if the sampled SM clock stayed
-        # at its maximum the burst figure is the denominator, otherwise the sustained one
+        # the conv launches are 0.1-0.4 ms bursts inside a ~1.3 ms step: if the sampled SM clock stayed at its
+        # maximum the burst figure is the denominator, otherwise the sustained one
         burst = clk["sm_mhz"] is not None and clk["sm_max_mhz"] and clk["sm_mhz"] >= 0.95 * clk["sm_max_mhz"]
         peaks = {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"] if burst else d["bf16_tflops_sustained"],
                  "src": "measured (burst)" if burst else "measured (sustained)"}
     conv_ms = per[1:].sum()
     conv_tflops = sum(flops) / (conv_ms * 1e-3) / 1e12
-    layers = [{"layer": i, "ms": float(per[i + 1]), "tflops": flops[i] / (per[i + 1] * 1e-3) / 1e12} for i in range(5)]
+    layer_rows = [{"layer": i, "ms": float(per[i + 1]), "tflops": flops[i] / (per[i + 1] * 1e-3) / 1e12} for i in range(5)]
 
     if rank == 0:
         from oracle import fovi_oracle as oracle
-        fx = fix_host.numpy().reshape(-1, 2)[: 64]
-        samp_bytes, mean_u = oracle.sampler_footprint_bytes(s["sampling_grid"], fx, np.full_like(fx, 256), 256, 256, 3, 4, 2)
+        fx = fix_host.numpy().reshape(-1, 2)[:64]
+        grid = retina.sampler.sampling_grid[0, 0].cpu().numpy()
+        samp_bytes, mean_u = oracle.sampler_footprint_bytes(grid, fx, np.full_like(fx, 256), 256, 256, 3, 4, 2)
         samp_bytes_per = samp_bytes / fx.shape[0]
         sampler_gbs = samp_bytes_per * M / (per[0] * 1e-3) / 1e9
         value = world * M * args.steps / (ms_total * 1e-3)
         e2e = world * M * args.steps / (ms_e2e * 1e-3)
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": {"workload": workload_name(args), "images_per_gpu": B, "fixations": F, "l2": "flushed between steps (192 MB write)"},
             "roofline": {"bound": "tensor", "kernel": "fovi_knnconv_tc_kernel (5 launches per step)", "achieved": conv_tflops, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": conv_tflops / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["src"],
                          "flops_per_launch_avg": sum(flops) / 5, "ms_per_launch_avg": conv_ms / 5},
-            "layers": layers,
+            "layers": layer_rows,
             "sampler": {"ms": float(per[0]), "algorithmic_bytes_per_imgfix": samp_bytes_per, "mean_unique_pixels": mean_u, "gbs": sampler_gbs,
                         "frac_of_hbm": sampler_gbs / peaks["hbm_gbs"]},
             "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 4 + fix_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 2,
-                    "ms_per_step": ms_e2e / args.steps},
+                    "ms_per_step": ms_e2e / args.steps, "chunks": args.chunks, "matches_device_path": e2e_matches},
             "gpu_launches": int(launches), "clocks": clk,
         }
         if world == 1 and not args.no_cpu_baseline:
-            v, dt = cpu_baseline(2, F, os.cpu_count())
-            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                                    "sample": f"2 images x {F} fixations per pass, float32 NumPy port of the reference path"}
+            line["cpu_baseline"] = cpu_baseline(F)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

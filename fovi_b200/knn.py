@@ -1,0 +1,226 @@
+"""KNNConv modules: drop-in counterparts of the reference's ``KNNConvLayer`` (fovi/arch/knn.py:401-720)
+and of the patch embeddings built on it (fovi/arch/knnvit.py:17-98, 224-290) on the CUDA kernels.
+
+Same constructor signatures, parameter names/shapes (``weight [C_out, C_in*V]`` c-major/v-minor,
+``bias [C_out]``: reference checkpoints load unchanged) and table attributes.  The forward pass runs the
+tensor-core kernel (bf16 operands, fp32 accumulation) or, with ``precision='fp32'``, the exact
+float32 kernel.  Inference only: the kernels implement no backward pass.
+"""
+import numpy as np
+import torch
+import torch.nn as nn
+
+from . import ops, tables
+from .coords import SamplingCoords, get_in_out_coords  # noqa: F401  (re-exported for callers of the reference API)
+
+__all__ = ["KNNConvLayer", "KNNPatchEmbedding", "KNNPartitioningPatchEmbedding", "KNNConvStack", "KNN_CONV_REGISTRY", "get_knn_conv_layer"]
+
+
+class KNNConvLayer(nn.Module):
+    """Convolution over the K nearest neighbours of each output point, filter taps assigned through a
+    per-neighbourhood reference frame.
+
+    Args as the reference (knn.py:423-430); ``precision`` ('bf16' | 'fp32') is an addition.
+    ``tables_override`` = dict(knn_indices [K,n_out] int64, tap [n_out,K], V, ref_coords?) skips the
+    table construction (used to run recorded tables).
+    """
+
+    def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True,
+                 bias=False, ref_frame_side_length=None, batch_size=None, precision="bf16", tables_override=None):
+        super().__init__()
+        if precision not in ("bf16", "fp32"):
+            raise ValueError("precision must be 'bf16' or 'fp32'")
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.in_coords, self.out_coords = in_coords, out_coords
+        self.device, self.arch_flag, self.sample_cortex = device, arch_flag, sample_cortex
+        self.ref_frame_side_length, self.batch_size, self.precision = ref_frame_side_length, batch_size, precision
+        n_in = in_coords.shape[0]
+        self.k = torch.minimum(torch.tensor(k), torch.tensor(n_in))
+        self._k = int(self.k.item())
+        if tables_override is None:
+            self.knn_indices, self.knn_distances, pts, cart = tables.knn_table(in_coords, out_coords, self._k, sample_cortex, batch_size)
+            self.ref_coords, self.ref_grid_size = tables.reference_frame(self._k, ref_frame_side_length, arch_flag, in_coords.dtype)
+            self.tap, self.knn_coords = tables.tap_table(self.knn_indices, pts, cart, out_coords, self.ref_coords, bool(sample_cortex))
+        else:
+            self.knn_indices = torch.as_tensor(np.asarray(tables_override["knn_indices"]), dtype=torch.long)
+            self.tap = torch.as_tensor(np.asarray(tables_override["tap"]).astype(np.int64))
+            self.knn_distances = self.knn_coords = None
+            V = int(tables_override["V"])
+            self.ref_grid_size = int(round(V ** 0.5))
+            self.ref_coords = tables_override.get("ref_coords", tables.reference_frame(self._k, self.ref_grid_size)[0] if self.ref_grid_size ** 2 == V else torch.zeros(V, 2))
+        self.knn_indices_pad_mask = self.knn_indices >= n_in
+        self.knn_indices_pad_token = tables.pad_token_table(self.knn_indices, n_in)
+        self.knn_indices_batch_cache = self.knn_indices_pad_token
+        V = self.ref_coords.shape[0]
+        self.weight = nn.Parameter(torch.empty(out_channels, in_channels * V))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_channels))
+        else:
+            self.register_parameter("bias", None)
+        nn.init.kaiming_normal_(self.weight)
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+        dev = torch.device(device)
+        self.to(dev)
+        self._plan = ops.KnnConvPlan(self.knn_indices_pad_token.numpy().astype(np.int32), self.tap.numpy().astype(np.uint16),
+                                     n_in, V, in_channels, out_channels, device=dev)
+        self._packed = {}          # dtype -> (weight version, data_ptr, packed tensor)
+
+    # ---- tables in the reference's own representation, built on demand (can be hundreds of MB)
+    @property
+    def local_rf(self):
+        """One-hot [n_out, K, V] float32, as the reference stores it (knn.py:636-647)."""
+        rf = torch.zeros(self.tap.shape[0], self.tap.shape[1], self.ref_coords.shape[0])
+        rf.scatter_(2, self.tap.unsqueeze(2), 1)
+        return rf
+
+    @property
+    def plan(self):
+        return self._plan
+
+    def packed_weight(self, dtype=torch.bfloat16):
+        """Kernel-layout copy of ``weight``, rebuilt when the parameter changes."""
+        w = self.weight
+        key = (w._version, w.data_ptr())
+        hit = self._packed.get(dtype)
+        if hit is None or hit[0] != key:
+            self._packed[dtype] = (key, self._plan.pack_weights(w.detach(), dtype))
+        return self._packed[dtype][1]
+
+    @torch.no_grad()
+    def forward_points(self, x_points, batch=None, relu=False, out_dtype=torch.bfloat16, out=None):
+        """Tensor-core path on the kernel layout: channels-last [B,n_in,cin_packed] bf16 (or the pair
+        layout with `batch` rows) -> channels-last [B,n_out,C_out]."""
+        return self._plan.forward(x_points, self.packed_weight(), self.bias, relu=relu, out_dtype=out_dtype, out=out, batch=batch)
+
+    def forward(self, X_l):
+        """X_l [B,C_in,N_in] -> [B,C_out,N_out] in X_l's dtype (knn.py:538-557); the result is a
+        channels-last view."""
+        if torch.is_grad_enabled() and X_l.requires_grad:
+            raise RuntimeError("fovi_b200.KNNConvLayer implements the forward pass only: call it under torch.no_grad() "
+                               "(for training keep the reference layer)")
+        with torch.no_grad():
+            return self._forward(X_l)
+
+    def _forward(self, X_l):
+        if self.precision == "fp32":
+            y = self._plan.forward_f32(X_l, self.packed_weight(torch.float32), self.bias)
+            return y.to(X_l.dtype)
+        out_dtype = torch.float32 if X_l.dtype == torch.float32 else torch.bfloat16
+        xp = ops.pack_points(X_l, self._plan)
+        y = self._plan.forward(xp, self.packed_weight(), self.bias, out_dtype=out_dtype, batch=X_l.shape[0])
+        return y.permute(0, 2, 1).to(X_l.dtype)
+
+    def load_conv2d_weights(self, conv2d, strict=False):
+        """Load a Conv2d kernel: transpose/flip from (row, col) to (x, y), resample to the reference
+        frame if sizes differ, flatten to [C_out, C_in*V] (knn.py:649-702)."""
+        w = conv2d.weight.data.clone().transpose(-1, -2).flip(-1)
+        g = self.ref_grid_size
+        if w.shape[0] != self.out_channels or w.shape[1] != self.in_channels:
+            raise ValueError("Conv2d channel counts do not match this layer")
+        if w.shape[2] != g or w.shape[3] != g:
+            if strict:
+                raise ValueError(f"Conv2d kernel {tuple(w.shape[2:])} != reference frame {g}x{g}")
+            w = nn.functional.interpolate(w, size=(g, g), mode="bilinear", align_corners=True)
+        self.weight.data.copy_(w.reshape(w.shape[0], -1))
+        if conv2d.bias is not None:
+            if self.bias is None:
+                raise ValueError("Conv2d has bias but layer does not. Recreate layer with bias=True.")
+            self.bias.data.copy_(conv2d.bias.data)
+
+    def __repr__(self):
+        return (f"{self.__class__.__name__}(\n\tin_channels={self.in_channels}\n\tout_channels={self.out_channels}\n\tk={self.k}\n\t"
+                f"n_ref={self.ref_coords.shape[0]}\n\tin_coords={self.in_coords}\n\tout_coords={self.out_coords}\n\tsample_cortex={self.sample_cortex}\n)")
+
+
+class KNNPatchEmbedding(KNNConvLayer):
+    """Foveated patch embedding: one KNNConv from the sensor points onto ~(cart_res/patch)^2 token points
+    (fovi/arch/knnvit.py:17-98).  forward returns [B, tokens, D] ([B, D, tokens] if `transposed`)."""
+
+    def __init__(self, in_channels, embed_dim, in_res, fov, cmf_a, style="isotropic", auto_match_cart_resources=True, in_cart_res=224,
+                 cart_patch_size=16, patch_overlap_factor=1, device="cuda", force_patches_less_than_matched=True,
+                 new_parameterization=False, transposed=False, max_coord_val=1, sample_cortex=True, ref_frame_side_length=None, **kwargs):
+        stride = cart_patch_size / patch_overlap_factor if new_parameterization else cart_patch_size
+        ic, oc, out_cart_res = get_in_out_coords(in_res, fov, cmf_a, stride, style=style, auto_match_cart_resources=auto_match_cart_resources,
+                                                 in_cart_res=in_cart_res, device="cpu", force_out_match_less_than=force_patches_less_than_matched,
+                                                 max_out_coord_val=max_coord_val)
+        k = cart_patch_size ** 2 if new_parameterization else int((cart_patch_size * out_cart_res / np.sqrt(len(oc)) * patch_overlap_factor) ** 2)
+        super().__init__(in_channels, embed_dim, k, ic, oc, device=device, sample_cortex=sample_cortex, ref_frame_side_length=ref_frame_side_length, **kwargs)
+        self.transposed = transposed
+
+    def forward(self, x):
+        if x.dim() == 4:
+            x = x.flatten(2)
+        tokens = super().forward(x)
+        return tokens if self.transposed else tokens.permute(0, 2, 1)
+
+
+class KNNPartitioningPatchEmbedding(KNNPatchEmbedding):
+    """Patch embedding whose K is the smallest neighbourhood size that lets the token neighbourhoods cover
+    every input point: inputs are partitioned by nearest token, and K is the largest count of inputs lying
+    closer to a token than its farthest partition member (fovi/arch/knnvit.py:224-290)."""
+
+    def __init__(self, in_channels, embed_dim, in_res, fov, cmf_a, style="isotropic", auto_match_cart_resources=True, in_cart_res=224,
+                 cart_patch_size=16, device="cuda", force_patches_less_than_matched=True, transposed=False, max_coord_val="auto",
+                 sample_cortex=True, **kwargs):
+        ic, oc, _ = get_in_out_coords(in_res, fov, cmf_a, cart_patch_size, style=style, auto_match_cart_resources=auto_match_cart_resources,
+                                      in_cart_res=in_cart_res, device="cpu", force_out_match_less_than=force_patches_less_than_matched,
+                                      max_out_coord_val=max_coord_val)
+        if sample_cortex == "geodesic":
+            raise NotImplementedError("geodesic neighbour ranking is not built; use sample_cortex=True")
+        pts = torch.cat([ic.cortical, ic.cortical_pad_coords], 0) if sample_cortex else torch.cat([ic.cartesian, ic.cartesian_pad_coords], 0)
+        dist = torch.cdist(pts, oc.cortical.clone() if sample_cortex else oc.cartesian)        # [n_in+pad, tokens]
+        owner = torch.argmin(dist[: len(ic)], 1)
+        k = 0
+        for t in range(len(oc)):
+            reach = dist[torch.argwhere(owner == t).squeeze(), t].max()
+            k = max(k, int((dist[:, t] < reach).sum()))
+        KNNConvLayer.__init__(self, in_channels, embed_dim, k, ic, oc, device=device, sample_cortex=sample_cortex, **kwargs)
+        self.transposed = transposed
+
+
+class KNNConvStack(nn.Module):
+    """A chain of KNNConv layers with ReLU between them, kept in the kernels' channels-last layout from
+    end to end (the conv -> activation skeleton of fovi/arch/knnalexnet.py:109-127).  Activation buffers
+    are allocated once per batch size and reused."""
+
+    def __init__(self, layers, final_relu=False):
+        super().__init__()
+        self.layers = nn.ModuleList(layers)
+        self.final_relu = final_relu
+        self._acts = {}
+
+    def _buffers(self, rows, device, out_dtype):
+        key = (rows, str(device), out_dtype)
+        if key not in self._acts:
+            n = len(self.layers)
+            self._acts[key] = [torch.empty((rows, L.plan.n_out, L.out_channels), dtype=out_dtype if i == n - 1 else torch.bfloat16, device=device)
+                               for i, L in enumerate(self.layers)]
+        return self._acts[key]
+
+    @torch.no_grad()
+    def forward_points(self, x_points, rows, out_dtype=torch.bfloat16):
+        """x_points: the first layer's kernel layout (see KNNConvLayer.forward_points) -> [rows, n_out, C_out]."""
+        bufs = self._buffers(rows, x_points.device, out_dtype)
+        h = x_points
+        for i, L in enumerate(self.layers):
+            last = i == len(self.layers) - 1
+            h = L.forward_points(h, batch=rows, relu=(not last) or self.final_relu, out=bufs[i])
+        return h
+
+    @torch.no_grad()
+    def forward(self, X):
+        """X [B,C_in,N_in] -> [B,C_out,N_out] (channels-last view), dtype of X."""
+        xp = ops.pack_points(X, self.layers[0].plan)
+        out_dtype = torch.float32 if X.dtype == torch.float32 else torch.bfloat16
+        return self.forward_points(xp, X.shape[0], out_dtype).permute(0, 2, 1)
+
+
+KNN_CONV_REGISTRY = {"default": KNNConvLayer, "b200": KNNConvLayer}
+
+
+def get_knn_conv_layer(name):
+    """Layer class by registry name (fovi/arch/knn.py:1014-1030)."""
+    if name not in KNN_CONV_REGISTRY:
+        raise ValueError(f"Unknown KNN conv layer: {name}. Available: {list(KNN_CONV_REGISTRY.keys())}")
+    return KNN_CONV_REGISTRY[name]

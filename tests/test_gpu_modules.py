@@ -1,0 +1,106 @@
+"""GPU: the module-level API (RetinalTransform / KNNConvLayer / patch embedding / KNNConvStack), built
+from this package's own geometry and tables, against the outputs recorded from the reference."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import synth_images, kaiming_weight
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def test_config1_sensor_plus_knnconv_modules(golden):
+    from fovi_b200.sensing import RetinalTransform
+    from fovi_b200.knn import KNNConvLayer
+    g = golden("config1.npz")
+    rt = RetinalTransform(resolution=64, start_res=224, fov=16, cmf_a=2.78, style="isotropic", sampler="grid_bilinear",
+                          fixation_size=224, auto_match_cart_resources=1, device="cuda")
+    assert rt.resolution == 44 and len(rt.sampler.coords) == 3975
+    x = torch.from_numpy(synth_images(0, (8, 3, 224, 224))).cuda()
+    y = rt(x, None)
+    assert y.shape == (8, 3, 3975) and np.array_equal(y.cpu().numpy(), g["sampled"])        # bit-exact vs the reference
+    c = rt.sampler.coords
+    w = kaiming_weight(np.random.RandomState(1), 64, 3, 49)
+    for precision, tol in (("fp32", 1e-5), ("bf16", 1e-2)):
+        layer = KNNConvLayer(3, 64, 49, c, c, device="cuda", ref_frame_side_length=7, bias=False, precision=precision)
+        assert np.array_equal(layer.knn_indices.numpy(), g["knn_idx"]) and np.array_equal(layer.tap.numpy(), g["tap"])
+        assert tuple(layer.weight.shape) == (64, 3 * 49) and layer.bias is None
+        layer.weight.data.copy_(torch.from_numpy(w))
+        out = layer(y)
+        assert out.shape == (8, 64, 3975) and out.dtype == torch.float32
+        assert rel_l2(out[0].cpu().numpy(), g["conv_out_b0"]) < tol
+        np.testing.assert_allclose(out.double().sum((1, 2)).cpu().numpy(), g["conv_out_sum"], rtol=5e-3, atol=5e-2)
+    rf = layer.local_rf
+    assert rf.shape == (3975, 49, 49) and float(rf.sum()) == 3975 * 49
+    # weight edits are picked up (the packed copy is rebuilt)
+    layer.weight.data.mul_(2)
+    assert rel_l2(layer(y)[0].cpu().numpy(), 2 * g["conv_out_b0"]) < 1e-2
+
+
+def test_multi_fixation_forward_matches_loop(golden):
+    from fovi_b200.sensing import RetinalTransform
+    g = golden("config2_small.npz")
+    rt = RetinalTransform(resolution=64, start_res=256, fov=16, cmf_a=1.0, sampler="grid_bilinear", fixation_size=256, device="cuda")
+    x = torch.from_numpy(synth_images(0, (2, 3, 256, 256))).cuda()
+    fix = torch.from_numpy(g["fix"]).cuda()
+    y = rt(x, fix)                                                     # [B,F,C,N] in one launch
+    assert np.array_equal(y.cpu().numpy(), g["a1_bilinear_near_zeros"])
+    for f in range(3):                                                 # the reference's per-fixation call pattern
+        assert torch.equal(rt(x, fix[:, f]), y[:, f])
+    ysz = rt(x, fix, fixation_size=torch.from_numpy(g["sizes"]).cuda())
+    assert np.array_equal(ysz.cpu().numpy(), g["a1_bilinear_near_sizes"])
+    rt_nn = RetinalTransform(resolution=64, start_res=256, fov=16, cmf_a=1.0, sampler="grid_nn", fixation_size=256, device="cuda")
+    assert np.array_equal(rt_nn(x, fix).cpu().numpy(), g["a1_nearest_near_zeros"])
+
+
+def test_config4_partitioning_patch_embedding(golden):
+    from fovi_b200.knn import KNNPartitioningPatchEmbedding
+    g = golden("config4_patch_embed_p8.npz")
+    pe = KNNPartitioningPatchEmbedding(3, 384, in_res=64, fov=16, cmf_a=2.78, in_cart_res=64, cart_patch_size=8, ref_frame_side_length=16,
+                                       max_coord_val="auto", sample_cortex=True, bias=True, transposed=True, device="cuda")
+    assert pe._k == g["knn_idx"].shape[0] == 105 and len(pe.out_coords) == 63
+    assert np.array_equal(pe.out_coords.cartesian.cpu().numpy(), g["out_cartesian"])
+    assert np.array_equal(pe.knn_indices.numpy(), g["knn_idx"]) and np.array_equal(pe.tap.numpy(), g["tap"])
+    pe.weight.data.copy_(torch.from_numpy(kaiming_weight(np.random.RandomState(1), 384, 3, 256)))
+    pe.bias.data.copy_(torch.from_numpy((0.1 * np.random.RandomState(2).standard_normal(384)).astype(f32)))
+    x = torch.from_numpy(synth_images(0, (2, 3, 3975))).cuda()
+    out = pe(x)
+    assert out.shape == (2, 384, 63)
+    assert rel_l2(out.cpu().numpy(), g["out_b2"]) < 1e-2
+
+
+def test_config3_stack_module_end_to_end(golden):
+    """Sensor -> five-layer stack through the module API, tables built by this package."""
+    from fovi_b200.coords import auto_match_num_coords, get_in_out_coords
+    from fovi_b200.knn import KNNConvLayer, KNNConvStack
+    acts = golden("config3_acts_b2.npz")
+    chans, strides, ks = [3, 64, 192, 384, 256, 256], [2, 2, 1, 1, 1], [121, 25, 9, 9, 9]
+    in_res, cart_res = auto_match_num_coords(16, 1.0, 64, "isotropic", 1)
+    rs = np.random.RandomState(1)
+    layers = []
+    for i in range(5):
+        ic, oc, out_cart = get_in_out_coords(in_res, 16, 1.0, strides[i], auto_match_cart_resources=1, in_cart_res=cart_res)
+        side = int(np.ceil(2 * np.sqrt(ks[i])))
+        L = KNNConvLayer(chans[i], chans[i + 1], ks[i], ic, oc, device="cuda", ref_frame_side_length=side, bias=True)
+        L.weight.data.copy_(torch.from_numpy(kaiming_weight(rs, chans[i + 1], chans[i], side * side)))
+        layers.append(L)
+        in_res, cart_res = oc.resolution, out_cart
+    stack = KNNConvStack(layers)
+    x = torch.from_numpy(synth_images(0, (2, 3, 4010))).cuda()
+    out = stack(x)
+    assert out.shape == (2, 256, 225) and out.dtype == torch.float32
+    assert rel_l2(out.cpu().numpy(), acts["act4"]) < 1e-2
+    out2 = stack(x)
+    assert torch.equal(out, out2)
+
+
+def test_cpu_tensors_are_refused(golden):
+    from fovi_b200 import ops
+    plan = ops.SamplerPlan(golden("sensor_a1.npz")["sampling_grid"])
+    with pytest.raises(ValueError, match="no CPU path"):
+        ops.sample(plan, torch.zeros(1, 3, 8, 8), torch.zeros(1, 1, 2), torch.zeros(1, 1, 2))

@@ -100,3 +100,29 @@ def test_closed_form_handles_pad_and_collisions():
     c = oracle.knnconv_forward_closed_form(x, idx, tap, V, w, b)
     np.testing.assert_allclose(a, c, rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(a[:, :, 0], np.broadcast_to(b, (B, Cout)), rtol=1e-6)
+
+
+def test_c_oracle_against_golden_and_numpy(golden):
+    """The C restatement: sampler bit-exact against the reference's recorded outputs, KNNConv within float
+    summation-order error of them, and equal to the NumPy oracle on a small random case with pads/collisions."""
+    from oracle import c_oracle
+    g, s = golden("config1.npz"), golden("sensor_a2p78.npz")
+    x = synth_images(0, (8, 3, 224, 224))
+    y = c_oracle.retinal_sample(x, s["sampling_grid"], np.full((8, 1, 2), 0.5, f32), np.full((8, 1, 2), 224, f32))
+    assert np.array_equal(y[:, 0], g["sampled"])
+    g2, s1 = golden("config2_small.npz"), golden("sensor_a1.npz")
+    x2 = synth_images(0, (2, 3, 256, 256))
+    full = np.full((2, 3, 2), 256, f32)
+    for mode in ("bilinear", "nearest"):
+        assert np.array_equal(c_oracle.retinal_sample(x2, s1["sampling_grid"], g2["fix_any"], full, mode, "zeros"), g2[f"a1_{mode}_any_zeros"])
+        assert np.array_equal(c_oracle.retinal_sample(x2, s1["sampling_grid"], g2["fix_any"], full, mode, "border"), g2[f"a1_{mode}_any_border"])
+        assert np.array_equal(c_oracle.retinal_sample(x2, s1["sampling_grid"], g2["fix"], g2["sizes"], mode, "zeros"), g2[f"a1_{mode}_near_sizes"])
+    w = kaiming_weight(np.random.RandomState(1), 64, 3, 49)
+    out = c_oracle.knnconv_forward_closed_form(g["sampled"], g["knn_idx_pad"], g["tap"].astype(np.int64), 49, w)
+    assert rel_err(out[0], g["conv_out_b0"]) < 1e-4
+    rs = np.random.RandomState(7)
+    xs = rs.standard_normal((3, 5, 11)).astype(f32)
+    idx = rs.randint(0, 12, (6, 7)).astype(np.int32); tap = rs.randint(0, 4, (7, 6))
+    ws = rs.standard_normal((8, 20)).astype(f32); b = rs.standard_normal(8).astype(f32)
+    np.testing.assert_allclose(c_oracle.knnconv_forward_closed_form(xs, idx, tap, 4, ws, b, relu=True),
+                               oracle.knnconv_forward_closed_form(xs, idx, tap, 4, ws, b, relu=True), rtol=1e-4, atol=1e-5)
