@@ -57,6 +57,7 @@ struct TcArgs {
   const float* bias; void* Y; int* status;
   int kp, B, n_in, n_out, c_out, cp;
   int ct, n_ct, n_mt, nstage, relu, y_f32, total_items;
+  uint32_t acc_cols, tmem_cols;  // columns per accumulator (power of two >= ct) and allocated in total (two accumulators)
   const unsigned char* X; const unsigned char* Wt; const unsigned char* zero_block; int n_pairs;  // PAIRS mode
   uint32_t stage_bytes, table_bytes;
 };
@@ -166,7 +167,7 @@ __device__ __forceinline__ void decode_item(const TcArgs& a, int item, int& n, i
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, MODE == MODE_PAIRS ? 2 : 1)
 fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -193,8 +194,8 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int i = threadIdx.x; i < a.c_out; i += blockDim.x) bias_s[i] = a.bias ? __ldg(a.bias + i) : 0.f;
-  if (warp == 1) {  // allocate all 512 tensor-memory columns: two accumulators of up to 256
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&hdr->tmem_base)) : "memory");
+  if (warp == 1) {  // tensor memory for two accumulators (all 512 columns when the c_out tile is wider than 128)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)), "r"(a.tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -342,7 +343,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int steps = C64 ? cnt * chunks : (cnt * chunks + 7) / 8;
         if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem + acc * 256u;
+        const uint32_t d_tmem = tmem + acc * a.acc_cols;
         for (int st = 0; st < steps; ++st) {
           if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, a.status, 3)) { ok = false; break; }
           tc_fence_after();
@@ -391,7 +392,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const int row = mt * BM + q * 32 + lane;
       const int o0 = ctile * a.ct;
       const size_t y_off = ((size_t)row * a.n_out + n) * a.c_out + o0;
-      const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + acc * 256u;
+      const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + acc * a.acc_cols;
       // 64 accumulator columns per round: two 32-column tensor-memory loads in flight, one wait
       for (int c0 = 0; c0 < a.ct; c0 += 64) {
         uint32_t r[64];
@@ -440,7 +441,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
   }
 }
 
@@ -507,7 +508,13 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   a.stage_bytes = A_STAGE_BYTES + (uint32_t)ct * 128u;  // A: 128 rows x 128 B;  B: ct rows x 128 B (any mode)
   if (a.kp > 32 * TBQ) return FOVI_ERR_UNSUPPORTED;  // neighbour lists longer than 256 entries
   a.table_bytes = (2u * (((uint32_t)a.kp * 6u + 15u) & ~15u) + (uint32_t)p->c_out * 4u + 1023u) & ~1023u;
-  const uint32_t budget = 220u * 1024u - 2048u - a.table_bytes;
+  a.acc_cols = 32;
+  while ((int)a.acc_cols < ct) a.acc_cols <<= 1;
+  a.tmem_cols = 2 * a.acc_cols;
+  // Pair mode with a narrow c_out tile is bound by per-item latencies (short neighbour lists, small MMAs), not by
+  // bandwidth: two CTAs per SM, each with half the stages and a quarter of the tensor memory, overlap them.
+  const int ctas_per_sm = (pairs && a.tmem_cols <= 256) ? 2 : 1;
+  const uint32_t budget = (ctas_per_sm == 2 ? 110u : 220u) * 1024u - 2048u - a.table_bytes;
   a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
   if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;
   const size_t smem = 1024 /*align slack*/ + 1024 /*header*/ + a.table_bytes + (size_t)a.nstage * a.stage_bytes;
@@ -529,7 +536,7 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   if (rc) return rc;
 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = std::min(a.total_items, fovi::sm_count());
+  const int grid = std::min(a.total_items, ctas_per_sm * fovi::sm_count());
   if (pairs) {
     FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_PAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     fovi_knnconv_tc_kernel<MODE_PAIRS><<<grid, 192, smem, st>>>(tmA, tmB, a);
