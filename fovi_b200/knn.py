@@ -78,8 +78,18 @@ class KNNConvLayer(nn.Module):
     def plan(self):
         return self._plan
 
+    def refresh_weights(self):
+        """Drop the kernel-layout copies of ``weight``.  In-place updates of the parameter (optimizer steps,
+        ``load_state_dict``, ``with torch.no_grad(): w.copy_(...)``) are noticed through its version counter;
+        writes through ``weight.data`` bypass that counter, so call this after them."""
+        self._packed.clear()
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self._packed.clear()
+
     def packed_weight(self, dtype=torch.bfloat16):
-        """Kernel-layout copy of ``weight``, rebuilt when the parameter changes."""
+        """Kernel-layout copy of ``weight``, rebuilt when the parameter changes (see refresh_weights)."""
         w = self.weight
         key = (w._version, w.data_ptr())
         hit = self._packed.get(dtype)

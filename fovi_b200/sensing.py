@@ -20,12 +20,29 @@ _MODES = {"nearest": ops.NEAREST, "bilinear": ops.BILINEAR}
 _PADS = {"zeros": ops.PAD_ZEROS, "border": ops.PAD_BORDER}
 
 
+_CONST_CACHE = {}
+
+
 def _as_bf2(v, B, device, what):
-    """Fixation argument -> float32 CUDA tensor [B,F,2] plus whether a fixation axis was given."""
+    """Fixation argument -> float32 tensor [B,F,2] on `device` plus whether a fixation axis was given.
+    A tensor that already is float32 [B,F,2] on the device is passed through untouched; Python numbers and
+    tuples (the usual default arguments) are uploaded once and cached, so steady-state calls issue no
+    host->device copy and no extra kernel."""
     if isinstance(v, torch.Tensor):
+        if v.dim() == 3 and v.dtype == torch.float32 and v.device == torch.device(device) and v.is_contiguous() and v.shape[0] == B and v.shape[2] == 2:
+            return v.detach(), True
         t = v.detach().to(device=device, dtype=torch.float32)
     else:
-        t = torch.as_tensor(np.asarray(v, dtype=np.float32), device=device)
+        arr = np.asarray(v, dtype=np.float32)
+        if arr.size <= 2:
+            key = (arr.tobytes(), arr.shape, B, str(device))
+            if key not in _CONST_CACHE:
+                if len(_CONST_CACHE) > 64:
+                    _CONST_CACHE.clear()
+                pair = np.broadcast_to(arr.reshape(-1), (2,)) if arr.size == 2 else np.full(2, arr.reshape(-1)[0], np.float32)
+                _CONST_CACHE[key] = torch.as_tensor(np.ascontiguousarray(np.broadcast_to(pair, (B, 1, 2))), device=device)
+            return _CONST_CACHE[key], False
+        t = torch.as_tensor(arr, device=device)
     multi = False
     if t.dim() == 0:
         t = t.reshape(1, 1, 1).expand(B, 1, 2)
@@ -124,6 +141,7 @@ class RetinalTransform(nn.Module):
         self.sampler = GridSampler(fov, cmf_a, resolution, device=device, mode="nearest" if sampler == "grid_nn" else "bilinear",
                                    style=style, padding_mode=padding_mode)
         self.scatter_sizes = self.sampler.coords.get_scatter_sizes().cpu().numpy()
+        self._hw_cache = {}
 
     def _defaults(self, fix_loc, fixation_size):
         if fix_loc is None:
@@ -153,7 +171,7 @@ class RetinalTransform(nn.Module):
         fix_hw, _ = _as_bf2(fixation_size, B, x.device, "fixation_size")
         F = fix_rc.shape[1]
         if fix_hw.shape[1] != F:
-            fix_hw = fix_hw.expand(B, F, 2).contiguous()
+            fix_hw = self._expanded(fix_hw, B, F)
         if conv_plan is not None and conv_plan.x_layout == ops.X_PAIRS:
             y = self.sampler.sample(x, fix_rc, fix_hw, layout=ops.OUT_FB_PAIRS, out=out)
         else:
@@ -161,6 +179,17 @@ class RetinalTransform(nn.Module):
             y = self.sampler.sample(x, fix_rc, fix_hw, out_dtype=torch.bfloat16, layout=ops.OUT_FBNC, channel_stride=cp, out=out)
             y = y.reshape(F * B, y.shape[2], cp)
         return y, F * B
+
+    def _expanded(self, fix_hw, B, F):
+        """[B,1,2] -> contiguous [B,F,2]; the result for a cached constant is cached too."""
+        key = (fix_hw.data_ptr(), B, F)
+        hit = self._hw_cache.get(key)
+        if hit is None or hit[0] is not fix_hw:
+            if len(self._hw_cache) > 16:
+                self._hw_cache.clear()
+            hit = (fix_hw, fix_hw.expand(B, F, 2).contiguous())
+            self._hw_cache[key] = hit
+        return hit[1]
 
     def get_warp_params(self):
         return self.fov, self.cmf_a, self.resolution, self.fixation_size

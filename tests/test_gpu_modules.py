@@ -37,9 +37,16 @@ def test_config1_sensor_plus_knnconv_modules(golden):
         np.testing.assert_allclose(out.double().sum((1, 2)).cpu().numpy(), g["conv_out_sum"], rtol=5e-3, atol=5e-2)
     rf = layer.local_rf
     assert rf.shape == (3975, 49, 49) and float(rf.sum()) == 3975 * 49
-    # weight edits are picked up (the packed copy is rebuilt)
-    layer.weight.data.mul_(2)
+    # weight edits are picked up (the packed copy is rebuilt): tracked in-place updates automatically,
+    # writes through .data after refresh_weights()
+    with torch.no_grad():
+        layer.weight.mul_(2)
     assert rel_l2(layer(y)[0].cpu().numpy(), 2 * g["conv_out_b0"]) < 1e-2
+    layer.weight.data.mul_(0.5)
+    layer.refresh_weights()
+    assert rel_l2(layer(y)[0].cpu().numpy(), g["conv_out_b0"]) < 1e-2
+    layer.load_state_dict({"weight": torch.from_numpy(3 * w)})
+    assert rel_l2(layer(y)[0].cpu().numpy(), 3 * g["conv_out_b0"]) < 1e-2
 
 
 def test_multi_fixation_forward_matches_loop(golden):
