@@ -200,7 +200,7 @@ class KNNConvStack(nn.Module):
         self.final_relu = final_relu
         self._acts = {}
 
-    def _buffers(self, rows, device, out_dtype):
+    def _act_buffers(self, rows, device, out_dtype):
         key = (rows, str(device), out_dtype)
         if key not in self._acts:
             n = len(self.layers)
@@ -211,7 +211,7 @@ class KNNConvStack(nn.Module):
     @torch.no_grad()
     def forward_points(self, x_points, rows, out_dtype=torch.bfloat16):
         """x_points: the first layer's kernel layout (see KNNConvLayer.forward_points) -> [rows, n_out, C_out]."""
-        bufs = self._buffers(rows, x_points.device, out_dtype)
+        bufs = self._act_buffers(rows, x_points.device, out_dtype)
         h = x_points
         for i, L in enumerate(self.layers):
             last = i == len(self.layers) - 1
