@@ -37,134 +37,11 @@
 // Every wait is bounded: a wait that gives up raises a CTA-wide abort flag and a status word in
 // global memory (read back by fovi_knnconv_check); all roles then drain and leave normally, the
 // tensor memory is freed and the context stays usable.
-#include <cuda.h>
-#include <string.h>
+#include <stdlib.h>
 
-#include "knnconv_plan.cuh"
+#include "tc_common.cuh"
 
 namespace {
-
-constexpr int BM = 128;            // batch rows per tile (UMMA M)
-constexpr int MAX_STAGES = 8;
-constexpr uint32_t A_STAGE_BYTES = 16384;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;  // try_wait attempts before giving up
-
-enum { MODE_C8 = 0, MODE_C64 = 1, MODE_PAIRS = 2 };
-
-struct TcArgs {
-  // per-output-point lists: neighbours (idx, tap) in C8/C64 mode, input pairs (idx only) in PAIRS mode
-  const int* nbr_idx; const uint16_t* nbr_tap; const int* nbr_cnt;
-  const float* bias; void* Y; int* status;
-  int kp, B, n_in, n_out, c_out, cp;
-  int ct, n_ct, n_mt, nstage, relu, y_f32, total_items;
-  uint32_t acc_cols, tmem_cols;  // columns per accumulator (power of two >= ct) and allocated in total (two accumulators)
-  const unsigned char* X; const unsigned char* Wt; const unsigned char* zero_block; int n_pairs;  // PAIRS mode
-  uint32_t stage_bytes, table_bytes;
-};
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 255u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicCAS(status, 0, code);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
-}
-
-// Contiguous global -> shared bulk copy (16-byte aligned, size a multiple of 16).
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (K-major operand).  layout: 0 = no swizzle, 2 = 128-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
-  d |= (uint64_t)layout << 61;
-  return d;
-}
-
-// Shared-memory header at the 1024-aligned base of the dynamic allocation.
-struct SmemHeader {
-  uint64_t full[MAX_STAGES];
-  uint64_t empty[MAX_STAGES];
-  uint64_t acc_full[2];
-  uint64_t acc_empty[2];
-  uint64_t drain;
-  uint32_t tmem_base;
-  int abort_flag;
-};
-
-constexpr int TBQ = 8;  // table entries prefetched per producer lane: list pitch <= 32 * TBQ
-
-__device__ __forceinline__ void decode_item(const TcArgs& a, int item, int& n, int& mt, int& ctile) {
-  ctile = item % a.n_ct;
-  const int t = item / a.n_ct;
-  n = t % a.n_out;
-  mt = t / a.n_out;
-}
 
 template <int MODE>
 __global__ void __launch_bounds__(192, MODE == MODE_PAIRS ? 2 : 1)
@@ -463,8 +340,10 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
-              uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128) {
+}  // namespace
+
+int fovi::encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                    uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { fovi::g_last_cuda_error = "cuTensorMapEncodeTiled entry point not available"; return FOVI_ERR_CUDA; }
   cuuint64_t dims[3] = {d0, d1, d2};
@@ -481,8 +360,6 @@ int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_
   return FOVI_OK;
 }
 
-}  // namespace
-
 extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
                                     int y_dtype, int B, int relu, void* stream) {
   if (!p || B < 0 || !fovi::valid_dtype(y_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
@@ -494,6 +371,13 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   if (!ct) return FOVI_ERR_UNSUPPORTED;
   const int cp = p->cin_packed;
   const bool c64 = cp % 64 == 0 && p->x_layout != FOVI_X_PAIRS;
+  // 64-channel layers with more than one batch tile run on CTA pairs (half the weight traffic per SM);
+  // FOVI_B200_SINGLE_CTA=1 keeps the single-CTA kernel (for comparison runs).
+  static const bool single_only = getenv("FOVI_B200_SINGLE_CTA") != nullptr;
+  if (c64 && !single_only && B > BM && ct % 32 == 0) {
+    const int rc2 = fovi::launch_knnconv_tc_pair(p, X, Wt, bias, Y, y_dtype, B, relu, reinterpret_cast<cudaStream_t>(stream));
+    if (rc2 != FOVI_ERR_UNSUPPORTED) return rc2;
+  }
 
   TcArgs a;
   const bool pairs = p->x_layout == FOVI_X_PAIRS;
@@ -529,9 +413,9 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
     memset(&tmA, 0, sizeof(tmA)); memset(&tmB, 0, sizeof(tmB));
     rc = FOVI_OK;
   } else {
-    rc = encode_3d(&tmA, X, (uint64_t)cp, (uint64_t)p->n_in, (uint64_t)B, (uint64_t)cp * 2, (uint64_t)p->n_in * cp * 2, kc, 1, BM, c64);
+    rc = fovi::encode_3d(&tmA, X, (uint64_t)cp, (uint64_t)p->n_in, (uint64_t)B, (uint64_t)cp * 2, (uint64_t)p->n_in * cp * 2, kc, 1, BM, c64);
     if (rc) return rc;
-    rc = encode_3d(&tmB, Wt, (uint64_t)cp, (uint64_t)p->c_out, (uint64_t)p->V, (uint64_t)cp * 2, (uint64_t)p->c_out * cp * 2, kc, (uint32_t)ct, 1, c64);
+    rc = fovi::encode_3d(&tmB, Wt, (uint64_t)cp, (uint64_t)p->c_out, (uint64_t)p->V, (uint64_t)cp * 2, (uint64_t)p->c_out * cp * 2, kc, (uint32_t)ct, 1, c64);
   }
   if (rc) return rc;
 
