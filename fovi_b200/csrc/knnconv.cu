@@ -145,7 +145,7 @@ extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16
   // (2p, 2p+1).  A neighbour takes the free half of a slot of its pair, or opens a new slot (so a
   // table that lists the same input point twice still adds both taps).
   std::vector<int> pidx, pcnt;
-  std::vector<uint16_t> ptap;
+  std::vector<uint16_t> ptap, prun;
   if (c_in <= 4) {
     p->x_layout = FOVI_X_PAIRS;
     p->n_pairs = (n_in + 1) / 2;
@@ -181,12 +181,30 @@ extern "C" int fovi_knnconv_plan_create(const int32_t* knn_idx_pad, const uint16
       }
       pcnt[n] = (int)order.size();
     }
+    // Copy plan: inside every 8-slot stage, consecutive pair indices are consecutive 2 KB blocks of the
+    // activations, so each run moves with one copy; the unused tail of the last stage is one run of zeros.
+    prun.assign((size_t)n_out * p->sp, 0);
+    for (int n = 0; n < n_out; ++n) {
+      const int* row = &pidx[(size_t)n * p->sp];
+      for (int s0 = 0; s0 < p->sp; s0 += 8) {
+        int j = 0;
+        while (j < 8) {
+          int len = 1;
+          if (row[s0 + j] >= p->n_pairs) len = 8 - j;
+          else while (j + len < 8 && row[s0 + j + len] == row[s0 + j] + len && row[s0 + j + len] < p->n_pairs) ++len;
+          prun[(size_t)n * p->sp + s0 + j] = (uint16_t)len;
+          j += len;
+        }
+      }
+    }
   }
   cudaError_t e = cudaGetDevice(&p->device);
   if (e == cudaSuccess && p->x_layout == FOVI_X_PAIRS) {
     e = cudaMalloc(&p->pair_idx, sizeof(int) * pidx.size());
     if (e == cudaSuccess) e = cudaMalloc(&p->pair_cnt, sizeof(int) * n_out);
     if (e == cudaSuccess) e = cudaMalloc(&p->pair_tap, sizeof(uint16_t) * ptap.size());
+    if (e == cudaSuccess) e = cudaMalloc(&p->pair_run, sizeof(uint16_t) * prun.size());
+    if (e == cudaSuccess) e = cudaMemcpy(p->pair_run, prun.data(), sizeof(uint16_t) * prun.size(), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMalloc(&p->zero_block, 16384);
     if (e == cudaSuccess) e = cudaMemset(p->zero_block, 0, 16384);
     if (e == cudaSuccess) e = cudaMemcpy(p->pair_idx, pidx.data(), sizeof(int) * pidx.size(), cudaMemcpyHostToDevice);
@@ -219,6 +237,7 @@ extern "C" void fovi_knnconv_plan_destroy(fovi_knnconv_plan* p) {
   if (p->pair_cnt) cudaFree(p->pair_cnt);
   if (p->pair_tap) cudaFree(p->pair_tap);
   if (p->zero_block) cudaFree(p->zero_block);
+  if (p->pair_run) cudaFree(p->pair_run);
   delete p;
 }
 

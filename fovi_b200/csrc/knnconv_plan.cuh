@@ -33,6 +33,7 @@ struct fovi_knnconv_plan {
   int* pair_idx = nullptr;      // [n_out, sp] pair index; unused slots hold n_pairs (reads as zero)
   int* pair_cnt = nullptr;      // [n_out]
   uint16_t* pair_tap = nullptr; // [n_out, sp, 2] tap of the even / odd member, 0xFFFF = not a neighbour
+  uint16_t* pair_run = nullptr; // [n_out, sp] at the first slot of a run of consecutive pairs inside an 8-slot stage: the run's length; else 0
   void* zero_block = nullptr;   // 16 KB of zeros: the operand blocks read for unused pair slots
   int ct = 0;                   // c_out tile of the tensor-core path (UMMA N), 0 = unsupported c_out
 };

@@ -28,8 +28,9 @@
 //          [point pair][batch row][2 points x 4 channels], so the 128 batch rows of one pair are
 //          ONE contiguous 2 KB block that already is the un-swizzled core-matrix layout, and the
 //          weights are pre-gathered per output point and c_out tile so the eight slabs of a stage
-//          are one contiguous block too.  Both move with plain bulk copies (cp.async.bulk), one
-//          per lane of the producer warp, so the nine copies of a stage issue as one instruction.
+//          are one contiguous block too.  Both move with plain bulk copies (cp.async.bulk): the plan
+//          precomputed the runs of consecutive pairs of every stage, one copy each, and the lanes of the
+//          producer warp issue a stage's copies together (the copy-issue rate is what bounds this mode).
 //          One MMA (K=16) consumes two pairs = four neighbours.  Unused slots read a block of
 //          zeros; rows past the batch keep stale shared memory, which only reaches output rows
 //          that are never stored.
@@ -93,7 +94,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint16_t* tt = reinterpret_cast<uint16_t*>(tbl0 + (size_t)a.kp * 4);
       for (int k = lane; k < a.kp; k += 32) {
         ti[k] = __ldg(a.nbr_idx + (size_t)n * a.kp + k);
-        if (MODE != MODE_PAIRS) tt[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
+        tt[k] = __ldg(a.nbr_tap + (size_t)n * a.kp + k);
       }
       cnt = __ldg(a.nbr_cnt + n);
     }
@@ -112,7 +113,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int q = 0; q < TBQ; ++q) {
           const int k = lane + 32 * q;
           r_idx[q] = k < a.kp ? __ldg(a.nbr_idx + (size_t)n2 * a.kp + k) : 0;
-          r_tap[q] = (MODE != MODE_PAIRS && k < a.kp) ? __ldg(a.nbr_tap + (size_t)n2 * a.kp + k) : (uint16_t)0;
+          r_tap[q] = k < a.kp ? __ldg(a.nbr_tap + (size_t)n2 * a.kp + k) : (uint16_t)0;
         }
         cnt_next = __ldg(a.nbr_cnt + n2);
       }
@@ -136,8 +137,13 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           if (!ok) break;
           const uint32_t sa = stages0 + s * a.stage_bytes;
           if (lane < 8) {
-            const int pr = tb_idx[st * 8 + lane];  // unused tail slots hold n_pairs: they read zeros
-            bulk_load(sa + lane * 2048u, pr < a.n_pairs ? xt + (size_t)pr * 2048 : a.zero_block, 2048u, full);
+            // the plan marked the first slot of every run of consecutive pairs with the run's length (the unused
+            // tail, whose slots hold n_pairs, is one run of zeros): one copy per run
+            const uint32_t len = tb_tap[st * 8 + lane];
+            if (len) {
+              const int pr = tb_idx[st * 8 + lane];
+              bulk_load(sa + lane * 2048u, pr < a.n_pairs ? xt + (size_t)pr * 2048 : a.zero_block, len * 2048u, full);
+            }
           } else if (lane == 8) {
             bulk_load(sa + b_stage_off, wn + (size_t)st * b_bytes, b_bytes, full);
           }
@@ -190,7 +196,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
         for (int q = 0; q < TBQ; ++q) {
           const int k = lane + 32 * q;
-          if (k < a.kp) { ti[k] = r_idx[q]; if (MODE != MODE_PAIRS) tt[k] = r_tap[q]; }
+          if (k < a.kp) { ti[k] = r_idx[q]; tt[k] = r_tap[q]; }
         }
       }
       __syncwarp();
@@ -381,7 +387,7 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
 
   TcArgs a;
   const bool pairs = p->x_layout == FOVI_X_PAIRS;
-  a.nbr_idx = pairs ? p->pair_idx : p->nbr_idx; a.nbr_tap = pairs ? nullptr : p->nbr_tap; a.nbr_cnt = pairs ? p->pair_cnt : p->nbr_cnt;
+  a.nbr_idx = pairs ? p->pair_idx : p->nbr_idx; a.nbr_tap = pairs ? p->pair_run : p->nbr_tap; a.nbr_cnt = pairs ? p->pair_cnt : p->nbr_cnt;
   a.bias = bias; a.Y = Y; a.status = p->status;
   a.kp = pairs ? p->sp : p->kp; a.B = B; a.n_in = p->n_in; a.n_out = p->n_out; a.c_out = p->c_out; a.cp = cp;
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;

@@ -42,6 +42,7 @@ struct SampleArgs {
   int cp;        // channel stride of the points-major layouts (8 = 2 points x 4 channels in pair layout)
   int f_major;   // 1: output row = f*B + b, 0: b*F + f
   int pairs;     // 1: pair layout [ceil(rows/128)][ceil(N/2)][128 rows][2][4]
+  int pow2;      // 1: W and H are powers of two, so x / W == x * (1 / W) exactly
 };
 
 template <typename TIn, int PAD>
@@ -53,7 +54,7 @@ __device__ __forceinline__ float tap(const TIn* plane, long long sy, long long s
 // NC == false: out row is [C][N];  NC == true: out row is [N][cp] with channels >= C zeroed.
 // STAGE: stage the whole output row in shared memory before one coalesced store.
 template <typename TIn, typename TOut, int MODE, int PAD, bool NC, bool STAGE>
-__global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
+__global__ void __launch_bounds__(256, 3) fovi_sample_kernel(const SampleArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TOut* stage = reinterpret_cast<TOut*>(smem_raw);
 
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
   const float cx = __fmul_rn(fc, Wf), cy = __fmul_rn(fr, Hf);
   const float half_w = __fdiv_rn(fw, 2.f), half_h = __fdiv_rn(fh, 2.f);
   const float sxw = Wf * 0.5f, syh = Hf * 0.5f;  // exact
+  const float inv_w = 1.f / Wf, inv_h = 1.f / Hf; // exact when a.pow2 (the only case they are used in)
   const TIn* img_b = reinterpret_cast<const TIn*>(a.img) + (long long)b * a.sb;
   const int pitch = a.pairs ? 4 : a.cp;  // per-point element pitch of the points-major layouts
 
@@ -80,13 +82,15 @@ __global__ void __launch_bounds__(512) fovi_sample_kernel(const SampleArgs a) {
     __syncthreads();
   }
 
+#pragma unroll 2
   for (int i = threadIdx.x; i < a.N; i += blockDim.x) {
     const float2 g = __ldg(a.sorted_xy + i);
     const int n = __ldg(a.sorted_idx + i);
     float gx = __fadd_rn(__fmul_rn(g.x, half_w), cx);
     float gy = __fadd_rn(__fmul_rn(g.y, half_h), cy);
-    gx = __fsub_rn(__fdiv_rn(__fmul_rn(2.f, gx), Wf), 1.f);
-    gy = __fsub_rn(__fdiv_rn(__fmul_rn(2.f, gy), Hf), 1.f);
+    // division by a power of two is a multiplication by its exact reciprocal: same bits, far fewer instructions
+    gx = __fsub_rn(a.pow2 ? __fmul_rn(__fmul_rn(2.f, gx), inv_w) : __fdiv_rn(__fmul_rn(2.f, gx), Wf), 1.f);
+    gy = __fsub_rn(a.pow2 ? __fmul_rn(__fmul_rn(2.f, gy), inv_h) : __fdiv_rn(__fmul_rn(2.f, gy), Hf), 1.f);
     float ix = __fmaf_rn(__fadd_rn(gx, 1.f), sxw, -0.5f);
     float iy = __fmaf_rn(__fadd_rn(gy, 1.f), syh, -0.5f);
     if (PAD == FOVI_PAD_BORDER) {
@@ -153,10 +157,10 @@ int launch_sample(const SampleArgs& a, size_t stage_bytes, cudaStream_t st) {
   if (stage_bytes <= 200 * 1024) {
     auto k = fovi_sample_kernel<TIn, TOut, MODE, PAD, NC, true>;
     if (stage_bytes > 48 * 1024) FOVI_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_bytes));
-    k<<<grid, 512, stage_bytes, st>>>(a);
+    k<<<grid, 256, stage_bytes, st>>>(a);
   } else {
     if (a.pairs) return FOVI_ERR_UNSUPPORTED;  // the pair layout is only written from the staged row
-    fovi_sample_kernel<TIn, TOut, MODE, PAD, NC, false><<<grid, 512, 0, st>>>(a);
+    fovi_sample_kernel<TIn, TOut, MODE, PAD, NC, false><<<grid, 256, 0, st>>>(a);
   }
   return fovi::after_launch("fovi_sample_kernel");
 }
@@ -262,6 +266,7 @@ extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* im
   a.cp = nc ? out_channel_stride : C;
   a.f_major = (layout == FOVI_OUT_FBCN || layout == FOVI_OUT_FBNC || layout == FOVI_OUT_FB_PAIRS) ? 1 : 0;
   a.pairs = pairs ? 1 : 0;
+  a.pow2 = ((W & (W - 1)) == 0 && (H & (H - 1)) == 0) ? 1 : 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == FOVI_F32 && out_dtype == FOVI_F32) return dispatch_mode<float, float>(a, mode, pad, nc, st);
   if (dtype == FOVI_F32 && out_dtype == FOVI_BF16) return dispatch_mode<float, __nv_bfloat16>(a, mode, pad, nc, st);

@@ -52,7 +52,7 @@ class SamplerPlan:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and lib is not None:          # `lib` is already gone when the interpreter is shutting down
             lib.fovi_sampler_plan_destroy(h)
 
 
@@ -110,7 +110,7 @@ class KnnConvPlan:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and lib is not None:
             lib.fovi_knnconv_plan_destroy(h)
 
     def flops_per_image(self):
