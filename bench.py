@@ -26,6 +26,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 CHANS = [3, 64, 192, 384, 256, 256]
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of this workload at its default size
+# (256 images x 4 fixations; profiles/dram_traffic_bench_default.md): sampler, then the five KNNConv launches.
+NCU_DRAM_TRAFFIC_MB = {"sampler": 212.8, "conv": [364.8, 192.5, 217.8, 275.2, 201.5]}
 METRIC = "images x fixations/s through sensor+KNNConv"
 UNIT = "img*fix/s"
 
@@ -320,7 +323,9 @@ def main():
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": {"workload": workload_name(args), "images_per_gpu": B, "fixations": F, "l2": "flushed between steps (192 MB write)"},
             "roofline": {"bound": "tensor", "kernel": "fovi_knnconv_tc_kernel (5 launches per step)", "achieved": conv_tflops, "peak": peaks["bf16_tflops"],
-                         "unit": "TFLOP/s", "frac": conv_tflops / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["src"],
+                         "unit": "TFLOP/s", "frac": conv_tflops / peaks["bf16_tflops"],
+                         "traffic": (sum(NCU_DRAM_TRAFFIC_MB["conv"]) / 5 * 1e6) if (B, F) == (256, 4) else None,
+                         "traffic_note": "bytes per launch, mean of the five launches (ncu dram read+write)", "peak_source": peaks["src"],
                          "flops_per_launch_avg": sum(flops) / 5, "ms_per_launch_avg": conv_ms / 5},
             "layers": layer_rows,
             "sampler": {"ms": float(per[0]), "algorithmic_bytes_per_imgfix": samp_bytes_per, "mean_unique_pixels": mean_u, "gbs": sampler_gbs,
