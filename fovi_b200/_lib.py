@@ -34,6 +34,12 @@ SIGNATURES = {
     "fovi_knnconv_check": (C.c_int, [_P, _P]),
     "fovi_static_scratch_bytes": (C.c_int64, []),
     "fovi_knnconv_forward_bcn_static": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_fused_intermediate_bytes": (C.c_int64, [_P, C.c_int]),
+    "fovi_sample_knnconv_fused": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), _P, _P,
+                                            C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.c_int, C.c_int, _P]),
+    "fovi_knnpool_plan_create": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
+    "fovi_knnpool_plan_destroy": (None, [_P]),
+    "fovi_knnpool_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "fovi_launch_count": (C.c_int64, []),
 }
 

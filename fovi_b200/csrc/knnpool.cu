@@ -1,0 +1,87 @@
+// KNN pooling: max / mean / sum over the K nearest input points of every output point, pad neighbours
+// ignored (the reference pads with NaN and uses nan-aware reductions, fovi/arch/knn.py:345-371).
+// A pure gather-reduce, bound by HBM/L2 bandwidth: one thread per output element walks its K neighbours.
+// Threads are laid out along the contiguous dimension of the activations (channels for the channels-last
+// layout, points for the reference's [B,C,N]), so every neighbour read of a warp is one or two cache lines
+// (channels-last) or a short gather (points-last).  NaN inputs are skipped like pads, as nanmean/nansum do.
+#include <vector>
+
+#include "common.cuh"
+
+struct fovi_knnpool_plan {
+  int n_in = 0, n_out = 0, K = 0;
+  int* idx = nullptr;   // [n_out, K] neighbour indices, pad = n_in
+};
+
+namespace {
+
+template <typename T, int MODE>
+__global__ void knnpool_kernel(const T* __restrict__ X, T* __restrict__ Y, const int* __restrict__ idx, int B, int C, int n_in,
+                               int n_out, int K, int bnc) {
+  const long long total = (long long)B * C * n_out;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    int b, c, n;
+    if (bnc) { c = (int)(e % C); n = (int)((e / C) % n_out); b = (int)(e / ((long long)C * n_out)); }
+    else { n = (int)(e % n_out); c = (int)((e / n_out) % C); b = (int)(e / ((long long)C * n_out)); }
+    const int* nb = idx + (long long)n * K;
+    float acc = MODE == 0 ? -INFINITY : 0.f;
+    int cnt = 0;
+    for (int k = 0; k < K; ++k) {
+      const int j = __ldg(nb + k);
+      if (j >= n_in) continue;
+      const float v = ld_as_float(bnc ? X + ((long long)b * n_in + j) * C + c : X + ((long long)b * C + c) * n_in + j);
+      if (v != v) continue;   // NaN: ignored
+      if (MODE == 0) acc = fmaxf(acc, v); else acc += v;
+      ++cnt;
+    }
+    if (MODE == 1) acc = acc / (float)cnt;   // no valid neighbour: 0/0 = NaN, as nanmean
+    Y[e] = from_float<T>(acc);
+  }
+}
+
+}  // namespace
+
+extern "C" int fovi_knnpool_plan_create(const int32_t* knn_idx_pad, int n_in, int n_out, int K, fovi_knnpool_plan** out) {
+  if (!knn_idx_pad || !out || n_in <= 0 || n_out <= 0 || K <= 0) return FOVI_ERR_INVALID_ARGUMENT;
+  std::vector<int> t((size_t)n_out * K);
+  for (int k = 0; k < K; ++k)
+    for (int n = 0; n < n_out; ++n) {
+      const int j = knn_idx_pad[(size_t)k * n_out + n];
+      if (j < 0 || j > n_in) return FOVI_ERR_TABLE_RANGE;
+      t[(size_t)n * K + k] = j;
+    }
+  auto* p = new fovi_knnpool_plan();
+  p->n_in = n_in; p->n_out = n_out; p->K = K;
+  cudaError_t e = cudaMalloc(&p->idx, sizeof(int) * t.size());
+  if (e == cudaSuccess) e = cudaMemcpy(p->idx, t.data(), sizeof(int) * t.size(), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    if (p->idx) cudaFree(p->idx);
+    delete p;
+    return fovi::cuda_fail(e, "fovi_knnpool_plan_create");
+  }
+  *out = p;
+  return FOVI_OK;
+}
+
+extern "C" void fovi_knnpool_plan_destroy(fovi_knnpool_plan* p) {
+  if (!p) return;
+  if (p->idx) cudaFree(p->idx);
+  delete p;
+}
+
+extern "C" int fovi_knnpool_forward(const fovi_knnpool_plan* p, const void* X, int dtype, int layout, int B, int C, int mode,
+                                    void* Y, void* stream) {
+  if (!p || !fovi::valid_dtype(dtype) || B < 0 || C <= 0 || mode < 0 || mode > 2) return FOVI_ERR_INVALID_ARGUMENT;
+  if (layout != FOVI_ACT_BCN && layout != FOVI_ACT_BNC) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;
+  if (!X || !Y) return FOVI_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long total = (long long)B * C * p->n_out;
+  const int grid = (int)std::min<long long>((total + 255) / 256, (long long)fovi::sm_count() * 32);
+  const int bnc = layout == FOVI_ACT_BNC;
+#define RUN(T, M) knnpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)X, (T*)Y, p->idx, B, C, p->n_in, p->n_out, p->K, bnc)
+  if (dtype == FOVI_F32) { if (mode == 0) RUN(float, 0); else if (mode == 1) RUN(float, 1); else RUN(float, 2); }
+  else { if (mode == 0) RUN(__nv_bfloat16, 0); else if (mode == 1) RUN(__nv_bfloat16, 1); else RUN(__nv_bfloat16, 2); }
+#undef RUN
+  return fovi::after_launch("knnpool_kernel");
+}

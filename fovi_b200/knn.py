@@ -13,7 +13,39 @@ import torch.nn as nn
 from . import ops, tables
 from .coords import SamplingCoords, get_in_out_coords  # noqa: F401  (re-exported for callers of the reference API)
 
-__all__ = ["KNNConvLayer", "KNNPatchEmbedding", "KNNPartitioningPatchEmbedding", "KNNConvStack", "KNN_CONV_REGISTRY", "get_knn_conv_layer"]
+__all__ = ["KNNPoolingLayer", "KNNConvLayer", "KNNPatchEmbedding", "KNNPartitioningPatchEmbedding", "KNNConvStack", "KNN_CONV_REGISTRY", "get_knn_conv_layer"]
+
+
+class KNNPoolingLayer(nn.Module):
+    """Pooling over the K nearest neighbours; counterpart of the reference layer (fovi/arch/knn.py:276-397) for
+    the modes 'max', 'avg' and 'sum' ('gaussian' is not built).  forward(X [B,C,N_in]) -> [B,C,N_out]."""
+
+    def __init__(self, k, in_coords, out_coords, mode="max", device="cuda", sample_cortex=True, gauss_sigma=10, batch_size=None):
+        super().__init__()
+        if mode not in ops.POOL_MODES:
+            raise NotImplementedError(f"pooling mode {mode!r}: 'max', 'avg' and 'sum' are built")
+        self.in_coords, self.out_coords, self.device, self.mode = in_coords, out_coords, device, mode
+        self.sample_cortex, self.batch_size = sample_cortex, batch_size
+        n_in = in_coords.shape[0]
+        self.k = torch.minimum(torch.tensor(k), torch.tensor(n_in))
+        self._k = int(self.k.item())
+        self.knn_indices, self.knn_distances, _, _ = tables.knn_table(in_coords, out_coords, self._k, sample_cortex, batch_size)
+        self.knn_pad_token_val = n_in
+        self.knn_indices_pad_mask = self.knn_indices >= n_in
+        self.knn_indices_pad_token = tables.pad_token_table(self.knn_indices, n_in)
+        self._plan = ops.KnnPoolPlan(self.knn_indices_pad_token.numpy().astype(np.int32), n_in, device=torch.device(device))
+
+    @torch.no_grad()
+    def forward(self, X_l):
+        return self._plan.forward(X_l, self.mode, ops.ACT_BCN)
+
+    @torch.no_grad()
+    def forward_points(self, x_bnc):
+        """Channels-last [B,N_in,C] -> [B,N_out,C] (the layout between the KNNConv kernels)."""
+        return self._plan.forward(x_bnc, self.mode, ops.ACT_BNC)
+
+    def __repr__(self):
+        return f"KNNPoolingLayer(\n\tmode={self.mode}\n\tk={self.k}\n\tin_coords={self.in_coords}\n\tout_coords={self.out_coords}\n\tsample_cortex={self.sample_cortex}\n)"
 
 
 class KNNConvLayer(nn.Module):

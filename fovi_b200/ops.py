@@ -177,6 +177,63 @@ class KnnConvPlan:
             check(lib.fovi_knnconv_check(self._h, _stream()), "fovi_knnconv_check")
 
 
+def sample_knnconv_fused(splan, cplan, img, fix_rc, fix_hw, wt, bias=None, relu=False, mode=BILINEAR, pad=PAD_ZEROS,
+                         out_dtype=torch.bfloat16, intermediate=None, out=None):
+    """Sensor -> first KNNConv in one C call.  Returns ([F*B, n_out, c_out], intermediate buffer)."""
+    _need_cuda(img, fix_rc, fix_hw, wt, bias)
+    B, Cc, H, W = img.shape
+    F = fix_rc.shape[1]
+    need = lib.fovi_fused_intermediate_bytes(cplan._h, B * F)
+    if intermediate is None:
+        intermediate = torch.zeros(need // 2, dtype=torch.bfloat16, device=img.device)
+    assert intermediate.numel() * intermediate.element_size() >= need
+    if out is None:
+        out = torch.empty((B * F, cplan.n_out, cplan.c_out), dtype=out_dtype, device=img.device)
+    if bias is not None:
+        bias = bias.detach().to(torch.float32).contiguous()
+    strides = (C.c_int64 * 4)(*img.stride())
+    with torch.cuda.device(img.device):
+        check(lib.fovi_sample_knnconv_fused(splan._h, cplan._h, _ptr(img), _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc.contiguous()),
+                                            _ptr(fix_hw.contiguous()), F, mode, pad, _ptr(intermediate), _ptr(wt),
+                                            _ptr(bias) if bias is not None else None, _ptr(out), _dt(out.dtype), int(relu), _stream()),
+              "fovi_sample_knnconv_fused")
+    return out, intermediate
+
+
+POOL_MODES = {"max": 0, "avg": 1, "sum": 2}
+
+
+class KnnPoolPlan:
+    """Device copy of a pooling layer's neighbour table (fovi_knnpool_plan)."""
+
+    def __init__(self, knn_idx_pad, n_in, device=None):
+        idx = np.ascontiguousarray(np.asarray(knn_idx_pad, np.int32))
+        self.K, self.n_out = idx.shape
+        self.n_in = int(n_in)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib.fovi_knnpool_plan_create(idx.ctypes.data_as(C.c_void_p), self.n_in, self.n_out, self.K, C.byref(h)), "fovi_knnpool_plan_create")
+        self._h = h
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h and lib is not None:
+            lib.fovi_knnpool_plan_destroy(h)
+
+    def forward(self, x, mode="max", layout=ACT_BCN):
+        """x [B,C,n_in] (ACT_BCN) or [B,n_in,C] (ACT_BNC), float32 or bf16 -> same layout with n_out points."""
+        _need_cuda(x)
+        x = x.contiguous()
+        B = x.shape[0]
+        Cc = x.shape[1] if layout == ACT_BCN else x.shape[2]
+        assert (x.shape[2] if layout == ACT_BCN else x.shape[1]) == self.n_in, x.shape
+        y = torch.empty((B, Cc, self.n_out) if layout == ACT_BCN else (B, self.n_out, Cc), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib.fovi_knnpool_forward(self._h, _ptr(x), _dt(x.dtype), layout, B, Cc, POOL_MODES[mode], _ptr(y), _stream()), "fovi_knnpool_forward")
+        return y
+
+
 def pack_points(x, cp=8, x_layout=X_BNC):
     """x [B,C,N] float32/bf16 -> tensor-core input: [B,N,cp] bf16 (pad channels zero) or the pair
     layout [ceil(B/128),ceil(N/2),128,8].  Pass a KnnConvPlan as `cp` to get the layout that plan consumes."""

@@ -191,6 +191,34 @@ int fovi_knnconv_forward_f32(const fovi_knnconv_plan* plan, const void* X, int x
  * plan since the last check gave up on a wait; clears the word. */
 int fovi_knnconv_check(fovi_knnconv_plan* plan, void* stream);
 
+/* Sensor -> first KNNConv in one call (the multi-fixation loop of policies.py:266-277 followed by the
+ * first KNNConvLayer.forward of the backbone, knnalexnet.py:118-119): samples all F fixations straight
+ * into the layout `conv` consumes, in `intermediate` (caller-owned device scratch of
+ * fovi_fused_intermediate_bytes(conv, B*F) bytes; it stays L2 resident between the two kernels), then runs
+ * the tensor-core layer.  Output rows are ordered '(f b)'.  Requires the sampler's point count == conv's
+ * n_in and C == conv's c_in.  Other arguments as for fovi_sample_forward / fovi_knnconv_forward. */
+int64_t fovi_fused_intermediate_bytes(const fovi_knnconv_plan* conv, int rows);
+int fovi_sample_knnconv_fused(const fovi_sampler_plan* sampler, fovi_knnconv_plan* conv, const void* img, int dtype, int B,
+                              int C, int H, int W, const int64_t* img_strides, const float* fix_rc, const float* fix_hw,
+                              int F, int mode, int pad, void* intermediate, const void* Wt, const float* bias, void* Y,
+                              int y_dtype, int relu, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * KNN pooling.
+ * Replaces KNNPoolingLayer.forward (fovi/arch/knn.py:345-394) for the modes 'max', 'avg', 'sum':
+ * reduction over the K neighbours of each output point, pad neighbours (and NaN inputs) ignored.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct fovi_knnpool_plan fovi_knnpool_plan;
+typedef enum { FOVI_POOL_MAX = 0, FOVI_POOL_AVG = 1, FOVI_POOL_SUM = 2 } fovi_pool_mode;
+
+/* knn_idx_pad: HOST [K,n_out] int32 — KNNPoolingLayer.knn_indices_pad_token (knn.py:316-319). */
+int fovi_knnpool_plan_create(const int32_t* knn_idx_pad, int n_in, int n_out, int K, fovi_knnpool_plan** out);
+void fovi_knnpool_plan_destroy(fovi_knnpool_plan* plan);
+/* X: [B,C,n_in] (FOVI_ACT_BCN) or [B,n_in,C] (FOVI_ACT_BNC) of `dtype`; Y: same layout and dtype with n_out
+ * points.  An output point without any valid neighbour gives -inf (max), NaN (avg), 0 (sum), as the reference. */
+int fovi_knnpool_forward(const fovi_knnpool_plan* plan, const void* X, int dtype, int layout, int B, int C, int mode,
+                         void* Y, void* stream);
+
 /* Number of kernels this library has launched from the calling process (all entry points). */
 int64_t fovi_launch_count(void);
 

@@ -26,7 +26,7 @@ import numpy as np
 __all__ = [
     "transform_sampling_grid", "grid_sample", "retinal_sample", "sampler_footprint_bytes",
     "tap_table_from_local_rf", "knn_gather", "knnconv_forward", "knnconv_forward_closed_form",
-    "knnconv_stack", "knn_pool_max",
+    "knnconv_stack", "knn_pool_max", "knn_pool_avg", "knn_pool_sum",
 ]
 
 f32 = np.float32
@@ -249,3 +249,27 @@ def knn_pool_max(X, knn_idx_pad):
     Xp = np.concatenate([np.asarray(X, f32), np.full((B, C, 1), -np.inf, f32)], 2)
     K, Nout = knn_idx_pad.shape
     return Xp[:, :, knn_idx_pad.reshape(-1)].reshape(B, C, K, Nout).max(2)
+
+
+def _pool_gather(X, knn_idx_pad):
+    B, C, Nin = X.shape
+    Xp = np.concatenate([np.asarray(X, f32), np.full((B, C, 1), np.nan, f32)], 2)     # pad slot is NaN (knn.py:356)
+    K, Nout = knn_idx_pad.shape
+    return Xp[:, :, knn_idx_pad.reshape(-1)].reshape(B, C, K, Nout)
+
+
+def knn_pool_sum(X, knn_idx_pad):
+    """'sum' mode: nansum over the K neighbours (fovi/arch/knn.py:370-371), accumulated in order k = 0..K-1."""
+    g = _pool_gather(X, knn_idx_pad)
+    acc = np.zeros(g[:, :, 0].shape, f32)
+    for k in range(g.shape[2]):
+        acc = (acc + np.where(np.isnan(g[:, :, k]), f32(0), g[:, :, k])).astype(f32)
+    return acc
+
+
+def knn_pool_avg(X, knn_idx_pad):
+    """'avg' mode: nanmean over the K neighbours (fovi/arch/knn.py:365-366) = nansum / number of non-NaN."""
+    g = _pool_gather(X, knn_idx_pad)
+    cnt = (~np.isnan(g)).sum(2).astype(f32)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        return (knn_pool_sum(X, knn_idx_pad) / cnt).astype(f32)

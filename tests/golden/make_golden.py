@@ -231,7 +231,14 @@ def main():
     p_ref = pool(torch.from_numpy(xb)).numpy()
     idxp = pool.knn_indices_pad_token.numpy().astype(np.int32)
     assert np.array_equal(oracle.knn_pool_max(xb, idxp), p_ref)
-    save("pool_a0p5.npz", knn_idx_pad=idxp, out=p_ref, n_in=np.int64(len(ic)), n_out=np.int64(len(oc)))
+    extra = {}
+    for mode in ("avg", "sum"):
+        pm = knn.KNNPoolingLayer(9, ic, oc, mode=mode, device="cpu")
+        extra[f"out_{mode}"] = pm(torch.from_numpy(xb)).numpy()
+        o = getattr(oracle, f"knn_pool_{mode}")(xb, idxp)
+        assert np.allclose(o, extra[f"out_{mode}"], rtol=1e-6, atol=1e-7), mode
+    save("pool_a0p5.npz", knn_idx_pad=idxp, knn_idx=pool.knn_indices.numpy().astype(np.int32), out=p_ref, n_in=np.int64(len(ic)),
+         n_out=np.int64(len(oc)), **extra)
     print("point counts a=0.5 chain:", len(ic), len(oc))
 
 

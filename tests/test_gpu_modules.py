@@ -111,3 +111,21 @@ def test_cpu_tensors_are_refused(golden):
     plan = ops.SamplerPlan(golden("sensor_a1.npz")["sampling_grid"])
     with pytest.raises(ValueError, match="no CPU path"):
         ops.sample(plan, torch.zeros(1, 3, 8, 8), torch.zeros(1, 1, 2), torch.zeros(1, 1, 2))
+
+
+def test_fused_sample_knnconv_call_equals_two_calls(golden):
+    from fovi_b200 import ops
+    g, s = golden("config1.npz"), golden("sensor_a2p78.npz")
+    V = int(g["V"])
+    splan = ops.SamplerPlan(s["sampling_grid"])
+    cplan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], int(g["n_in"]), V, 3, 64)
+    wt = cplan.pack_weights(torch.from_numpy(kaiming_weight(np.random.RandomState(1), 64, 3, V)).cuda())
+    B, F = 5, 3
+    x = torch.from_numpy(synth_images(2, (B, 3, 224, 224))).cuda()
+    fix = torch.from_numpy((0.3 + 0.4 * np.random.RandomState(3).random_sample((B, F, 2))).astype(f32)).cuda()
+    hw = torch.full((B, F, 2), 224.0, device="cuda")
+    y, inter = ops.sample_knnconv_fused(splan, cplan, x, fix, hw, wt, relu=True, out_dtype=torch.float32)
+    xin = ops.sample(splan, x, fix, hw, layout=ops.OUT_FB_PAIRS)
+    want = cplan.forward(xin, wt, relu=True, out_dtype=torch.float32, batch=B * F)
+    cplan.check()
+    assert y.shape == (B * F, 3975, 64) and torch.equal(y, want)

@@ -126,3 +126,10 @@ def test_c_oracle_against_golden_and_numpy(golden):
     ws = rs.standard_normal((8, 20)).astype(f32); b = rs.standard_normal(8).astype(f32)
     np.testing.assert_allclose(c_oracle.knnconv_forward_closed_form(xs, idx, tap, 4, ws, b, relu=True),
                                oracle.knnconv_forward_closed_form(xs, idx, tap, 4, ws, b, relu=True), rtol=1e-4, atol=1e-5)
+
+
+def test_pool_avg_sum(golden):
+    g = golden("pool_a0p5.npz")
+    x = synth_images(5, (2, 4, int(g["n_in"]))) - f32(0.5)
+    np.testing.assert_allclose(oracle.knn_pool_avg(x, g["knn_idx_pad"]), g["out_avg"], rtol=1e-6, atol=1e-7)
+    np.testing.assert_allclose(oracle.knn_pool_sum(x, g["knn_idx_pad"]), g["out_sum"], rtol=1e-6, atol=1e-7)
