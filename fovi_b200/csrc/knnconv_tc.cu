@@ -45,7 +45,7 @@
 namespace {
 
 template <int MODE>
-__global__ void __launch_bounds__(192, MODE == MODE_PAIRS ? 2 : 1)
+__global__ void __launch_bounds__(192, MODE == MODE_PAIRS ? 3 : 1)
 fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcArgs a) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -401,10 +401,12 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   a.acc_cols = 32;
   while ((int)a.acc_cols < ct) a.acc_cols <<= 1;
   a.tmem_cols = 2 * a.acc_cols;
-  // Pair mode with a narrow c_out tile is bound by per-item latencies (short neighbour lists, small MMAs), not by
-  // bandwidth: two CTAs per SM, each with half the stages and a quarter of the tensor memory, overlap them.
-  const int ctas_per_sm = (pairs && a.tmem_cols <= 256) ? 2 : 1;
-  const uint32_t budget = (ctas_per_sm == 2 ? 110u : 220u) * 1024u - 2048u - a.table_bytes;
+  // Pair mode with a narrow c_out tile is bound by per-item latencies (copy issue, short neighbour lists, small MMAs),
+  // not by bandwidth: up to three CTAs per SM, each with fewer stages and a share of the tensor memory, overlap them
+  // (measured on the 3->64 first layer: 0.29 / 0.17 / 0.16 ms with 1 / 2 / 3 CTAs per SM).  FOVI_B200_PAIR_CTAS overrides.
+  static const int pair_ctas = getenv("FOVI_B200_PAIR_CTAS") ? atoi(getenv("FOVI_B200_PAIR_CTAS")) : 3;
+  const int ctas_per_sm = !pairs ? 1 : (a.tmem_cols <= 128 && pair_ctas >= 3) ? 3 : (a.tmem_cols <= 256 && pair_ctas >= 2) ? 2 : 1;
+  const uint32_t budget = (ctas_per_sm == 3 ? 73u : ctas_per_sm == 2 ? 110u : 220u) * 1024u - 2048u - a.table_bytes;
   a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
   if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;
   const size_t smem = 1024 /*align slack*/ + 1024 /*header*/ + a.table_bytes + (size_t)a.nstage * a.stage_bytes;
