@@ -17,15 +17,31 @@
 //   re-associating any of it, which is what makes float32 results bit-identical to the CPU
 //   reference.
 #include <algorithm>
+#include <mutex>
+#include <type_traits>
+#include <stdlib.h>
+#include <string.h>
 #include <vector>
 
 #include "common.cuh"
+
+constexpr int MAX_TEX = 16;
+
+// Texture objects over one image buffer (see the texture path below), remembered so that a buffer that comes back
+// (a pre-allocated input, the slots of a copy pipeline) costs nothing to bind again.
+struct TexBinding {
+  const void* ptr = nullptr;
+  int B = 0, C = 0, H = 0, W = 0, images_per_tex = 0, n_tex = 0;
+  cudaTextureObject_t tex[MAX_TEX] = {};
+};
 
 struct fovi_sampler_plan {
   int n_points = 0;
   int device = -1;
   float2* sorted_xy = nullptr;  // [N] grid (x, y) in visiting order
   int* sorted_idx = nullptr;    // [N] original index of each visited point
+  std::mutex tex_mutex;
+  std::vector<TexBinding> tex_cache;   // most recently used last, at most 8
 };
 
 namespace {
@@ -43,6 +59,8 @@ struct SampleArgs {
   int f_major;   // 1: output row = f*B + b, 0: b*F + f
   int pairs;     // 1: pair layout [ceil(rows/128)][ceil(N/2)][128 rows][2][4]
   int pow2;      // 1: W and H are powers of two, so x / W == x * (1 / W) exactly
+  int images_per_tex;                  // texture path: images covered by each texture object
+  cudaTextureObject_t tex[MAX_TEX];    // texture path: the image planes as 2-D textures of height images*C*H
 };
 
 template <typename TIn, int PAD>
@@ -53,7 +71,14 @@ __device__ __forceinline__ float tap(const TIn* plane, long long sy, long long s
 
 // NC == false: out row is [C][N];  NC == true: out row is [N][cp] with channels >= C zeroed.
 // STAGE: stage the whole output row in shared memory before one coalesced store.
-template <typename TIn, typename TOut, int MODE, int PAD, bool NC, bool STAGE>
+// TEX (float32 contiguous NCHW images, bilinear): the 2x2 footprint of a point in one channel plane is fetched with
+// ONE texture gather (tex2Dgather returns the four raw texels a bilinear fetch would blend; the blend itself stays
+// in the float32 code below, so results are unchanged bit for bit).  Twelve scattered 4-byte loads per point become
+// three gathers on the texture path, which is built for exactly this 2-D footprint; the L1 data pipe that bounds the
+// plain-load variant is relieved.  A texture covers the planes of `images_per_tex` images stacked along y, so rows
+// outside [0,H) would fall into a neighbouring plane: they are masked here; columns outside [0,W) read 0 through the
+// border address mode.
+template <typename TIn, typename TOut, int MODE, int PAD, bool NC, bool STAGE, bool TEX = false>
 __global__ void __launch_bounds__(256, 3) fovi_sample_kernel(const SampleArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TOut* stage = reinterpret_cast<TOut*>(smem_raw);
@@ -110,13 +135,23 @@ __global__ void __launch_bounds__(256, 3) fovi_sample_kernel(const SampleArgs a)
       const float w_nw = __fmul_rn(uy, ux), w_ne = __fmul_rn(uy, tx);
       const float w_sw = __fmul_rn(ty, ux), w_se = __fmul_rn(ty, tx);
       const int x0 = (int)x0f, y0 = (int)y0f;
+      const bool top = y0 >= 0 && y0 < a.H, bot = y0 + 1 >= 0 && y0 + 1 < a.H;
+      const cudaTextureObject_t tex = TEX ? a.tex[b / a.images_per_tex] : 0;
+      const int plane0 = TEX ? (b % a.images_per_tex) * a.C : 0;
 #pragma unroll 3
       for (int c = 0; c < a.C; ++c) {
-        const TIn* plane = img_b + c * a.sc;
-        const float v_nw = tap<TIn, PAD>(plane, a.sy, a.sx, x0, y0, a.W, a.H);
-        const float v_ne = tap<TIn, PAD>(plane, a.sy, a.sx, x0 + 1, y0, a.W, a.H);
-        const float v_sw = tap<TIn, PAD>(plane, a.sy, a.sx, x0, y0 + 1, a.W, a.H);
-        const float v_se = tap<TIn, PAD>(plane, a.sy, a.sx, x0 + 1, y0 + 1, a.W, a.H);
+        float v_nw, v_ne, v_sw, v_se;
+        if (TEX) {
+          // footprint of (x, y) is texels floor(x-0.5), +1: aim at the middle of the range that selects x0 / y0
+          const float4 q = tex2Dgather<float4>(tex, (float)x0 + 1.0f, (float)((plane0 + c) * a.H + y0) + 1.0f, 0);
+          v_nw = top ? q.w : 0.f; v_ne = top ? q.z : 0.f; v_sw = bot ? q.x : 0.f; v_se = bot ? q.y : 0.f;
+        } else {
+          const TIn* plane = img_b + c * a.sc;
+          v_nw = tap<TIn, PAD>(plane, a.sy, a.sx, x0, y0, a.W, a.H);
+          v_ne = tap<TIn, PAD>(plane, a.sy, a.sx, x0 + 1, y0, a.W, a.H);
+          v_sw = tap<TIn, PAD>(plane, a.sy, a.sx, x0, y0 + 1, a.W, a.H);
+          v_se = tap<TIn, PAD>(plane, a.sy, a.sx, x0 + 1, y0 + 1, a.W, a.H);
+        }
         float acc = __fmul_rn(v_nw, w_nw);
         acc = __fmaf_rn(v_ne, w_ne, acc);
         acc = __fmaf_rn(v_sw, w_sw, acc);
@@ -154,6 +189,14 @@ __global__ void __launch_bounds__(256, 3) fovi_sample_kernel(const SampleArgs a)
 template <typename TIn, typename TOut, int MODE, int PAD, bool NC>
 int launch_sample(const SampleArgs& a, size_t stage_bytes, cudaStream_t st) {
   const int grid = a.B * a.F;
+  if constexpr (std::is_same<TIn, float>::value && MODE == FOVI_BILINEAR) {
+    if (a.images_per_tex > 0 && stage_bytes <= 200 * 1024) {
+      auto k = fovi_sample_kernel<TIn, TOut, MODE, PAD, NC, true, true>;
+      if (stage_bytes > 48 * 1024) FOVI_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_bytes));
+      k<<<grid, 256, stage_bytes, st>>>(a);
+      return fovi::after_launch("fovi_sample_kernel(tex)");
+    }
+  }
   if (stage_bytes <= 200 * 1024) {
     auto k = fovi_sample_kernel<TIn, TOut, MODE, PAD, NC, true>;
     if (stage_bytes > 48 * 1024) FOVI_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stage_bytes));
@@ -192,6 +235,70 @@ uint32_t morton16(uint32_t x, uint32_t y) {
     return v;
   };
   return spread(x) | (spread(y) << 1);
+}
+
+// Binds (or finds) texture objects over a contiguous float32 [B,C,H,W] buffer.  Returns false when the buffer does not
+// qualify (alignment, size limits) — the caller then uses the plain-load kernel.
+bool bind_textures(fovi_sampler_plan* plan, const void* img, int B, int C, int H, int W, SampleArgs& a) {
+  static const bool disabled = getenv("FOVI_B200_NO_TEXTURE") != nullptr;
+  if (disabled) return false;
+  int dev = 0, max_h = 0, max_w = 0, pitch_align = 0, tex_align = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  cudaDeviceGetAttribute(&max_h, cudaDevAttrMaxTexture2DLinearHeight, dev);
+  cudaDeviceGetAttribute(&max_w, cudaDevAttrMaxTexture2DLinearWidth, dev);
+  cudaDeviceGetAttribute(&pitch_align, cudaDevAttrTexturePitchAlignment, dev);
+  cudaDeviceGetAttribute(&tex_align, cudaDevAttrTextureAlignment, dev);
+  if (pitch_align <= 0 || tex_align <= 0) return false;
+  const size_t pitch = (size_t)W * 4, image_bytes = (size_t)C * H * pitch;
+  const long long rows_per_image = (long long)C * H;
+  if (W > max_w || rows_per_image > max_h || pitch % pitch_align || image_bytes % tex_align ||
+      (reinterpret_cast<uintptr_t>(img) % tex_align) || rows_per_image * 1 >= (1 << 24))
+    return false;
+  const int per_tex = (int)std::min<long long>(B, std::min<long long>(max_h, (1 << 24) - 2) / rows_per_image);
+  const int n_tex = (B + per_tex - 1) / per_tex;
+  if (n_tex > MAX_TEX) return false;
+  std::lock_guard<std::mutex> lock(plan->tex_mutex);
+  for (size_t i = 0; i < plan->tex_cache.size(); ++i) {
+    TexBinding& t = plan->tex_cache[i];
+    if (t.ptr == img && t.B == B && t.C == C && t.H == H && t.W == W) {
+      a.images_per_tex = t.images_per_tex;
+      for (int k = 0; k < t.n_tex; ++k) a.tex[k] = t.tex[k];
+      std::rotate(plan->tex_cache.begin() + i, plan->tex_cache.begin() + i + 1, plan->tex_cache.end());
+      return true;
+    }
+  }
+  TexBinding t;
+  t.ptr = img; t.B = B; t.C = C; t.H = H; t.W = W; t.images_per_tex = per_tex; t.n_tex = n_tex;
+  for (int k = 0; k < n_tex; ++k) {
+    const int images = std::min(per_tex, B - k * per_tex);
+    cudaResourceDesc rd;
+    memset(&rd, 0, sizeof(rd));
+    rd.resType = cudaResourceTypePitch2D;
+    rd.res.pitch2D.devPtr = const_cast<char*>(static_cast<const char*>(img)) + (size_t)k * per_tex * image_bytes;
+    rd.res.pitch2D.desc = cudaCreateChannelDesc<float>();
+    rd.res.pitch2D.width = W;
+    rd.res.pitch2D.height = (size_t)images * rows_per_image;
+    rd.res.pitch2D.pitchInBytes = pitch;
+    cudaTextureDesc td;
+    memset(&td, 0, sizeof(td));
+    td.addressMode[0] = td.addressMode[1] = cudaAddressModeBorder;
+    td.filterMode = cudaFilterModePoint;
+    td.readMode = cudaReadModeElementType;
+    td.normalizedCoords = 0;
+    if (cudaCreateTextureObject(&t.tex[k], &rd, &td, nullptr) != cudaSuccess) {
+      cudaGetLastError();
+      for (int j = 0; j < k; ++j) cudaDestroyTextureObject(t.tex[j]);
+      return false;
+    }
+  }
+  if (plan->tex_cache.size() >= 8) {
+    for (int k = 0; k < plan->tex_cache.front().n_tex; ++k) cudaDestroyTextureObject(plan->tex_cache.front().tex[k]);
+    plan->tex_cache.erase(plan->tex_cache.begin());
+  }
+  plan->tex_cache.push_back(t);
+  a.images_per_tex = per_tex;
+  for (int k = 0; k < n_tex; ++k) a.tex[k] = t.tex[k];
+  return true;
 }
 
 }  // namespace
@@ -234,6 +341,8 @@ extern "C" void fovi_sampler_plan_destroy(fovi_sampler_plan* plan) {
   if (!plan) return;
   if (plan->sorted_xy) cudaFree(plan->sorted_xy);
   if (plan->sorted_idx) cudaFree(plan->sorted_idx);
+  for (auto& t : plan->tex_cache)
+    for (int k = 0; k < t.n_tex; ++k) cudaDestroyTextureObject(t.tex[k]);
   delete plan;
 }
 
@@ -267,6 +376,9 @@ extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* im
   a.f_major = (layout == FOVI_OUT_FBCN || layout == FOVI_OUT_FBNC || layout == FOVI_OUT_FB_PAIRS) ? 1 : 0;
   a.pairs = pairs ? 1 : 0;
   a.pow2 = ((W & (W - 1)) == 0 && (H & (H - 1)) == 0) ? 1 : 0;
+  a.images_per_tex = 0;
+  if (dtype == FOVI_F32 && mode == FOVI_BILINEAR && a.sx == 1 && a.sy == W && a.sc == (long long)H * W && a.sb == (long long)C * H * W)
+    bind_textures(const_cast<fovi_sampler_plan*>(plan), img, B, C, H, W, a);   // leaves images_per_tex = 0 when not applicable
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == FOVI_F32 && out_dtype == FOVI_F32) return dispatch_mode<float, float>(a, mode, pad, nc, st);
   if (dtype == FOVI_F32 && out_dtype == FOVI_BF16) return dispatch_mode<float, __nv_bfloat16>(a, mode, pad, nc, st);
