@@ -71,11 +71,17 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = threadIdx.x; i < a.c_out; i += blockDim.x) bias_s[i] = a.bias ? __ldg(a.bias + i) : 0.f;
   if (warp == 1) {  // tensor memory for two accumulators (all 512 columns when the c_out tile is wider than 128)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&hdr->tmem_base)), "r"(a.tmem_cols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // Programmatic dependent launch: let the next kernel of the stream be scheduled onto SMs as they free up (its
+  // prologue then overlaps this kernel's tail), and hold this kernel's own first read of global data until the
+  // kernel before it has completed.  Everything above (barriers, tensor memory) needed no global data.  Both are
+  // no-ops when the kernel was launched without the attribute.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = threadIdx.x; i < a.c_out; i += blockDim.x) bias_s[i] = a.bias ? __ldg(a.bias + i) : 0.f;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -431,13 +437,13 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   const int grid = std::min(a.total_items, ctas_per_sm * fovi::sm_count());
   if (pairs) {
     FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_PAIRS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fovi_knnconv_tc_kernel<MODE_PAIRS><<<grid, 192, smem, st>>>(tmA, tmB, a);
+    FOVI_CUDA(fovi::launch_pdl(fovi_knnconv_tc_kernel<MODE_PAIRS>, grid, 192, smem, st, tmA, tmB, a));
   } else if (c64) {
     FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_C64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fovi_knnconv_tc_kernel<MODE_C64><<<grid, 192, smem, st>>>(tmA, tmB, a);
+    FOVI_CUDA(fovi::launch_pdl(fovi_knnconv_tc_kernel<MODE_C64>, grid, 192, smem, st, tmA, tmB, a));
   } else {
     FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_kernel<MODE_C8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    fovi_knnconv_tc_kernel<MODE_C8><<<grid, 192, smem, st>>>(tmA, tmB, a);
+    FOVI_CUDA(fovi::launch_pdl(fovi_knnconv_tc_kernel<MODE_C8>, grid, 192, smem, st, tmA, tmB, a));
   }
   return fovi::after_launch("fovi_knnconv_tc_kernel");
 }

@@ -94,11 +94,17 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = threadIdx.x; i < a.c_out; i += blockDim.x) bias_s[i] = a.bias ? __ldg(a.bias + i) : 0.f;
   if (warp == 1) {  // both CTAs of the pair allocate together: 512 columns = two accumulators of up to 256
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&hdr->tmem_base)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
+  // Programmatic dependent launch: let the next kernel of the stream be scheduled onto SMs as they free up (its
+  // prologue then overlaps this kernel's tail), and hold this kernel's own first read of global data until the
+  // kernel before it has completed.  Everything above (barriers, tensor memory) needed no global data.  Both are
+  // no-ops when the kernel was launched without the attribute.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = threadIdx.x; i < a.c_out; i += blockDim.x) bias_s[i] = a.bias ? __ldg(a.bias + i) : 0.f;
   tc_fence_before();
   cluster_sync_all();   // barriers of both CTAs are initialised before anyone signals across
   tc_fence_after();
@@ -313,6 +319,6 @@ int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, cons
 
   FOVI_CUDA(cudaFuncSetAttribute(fovi_knnconv_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int pairs = (int)std::min<long long>(items, sms / 2);
-  fovi_knnconv_tc_pair_kernel<<<2 * pairs, 192, smem, st>>>(tmA, tmB, a);   // cluster size 2 comes from __cluster_dims__
+  FOVI_CUDA(fovi::launch_pdl(fovi_knnconv_tc_pair_kernel, 2 * pairs, 192, smem, st, tmA, tmB, a));   // cluster size 2 comes from __cluster_dims__
   return fovi::after_launch("fovi_knnconv_tc_pair_kernel");
 }

@@ -2,7 +2,9 @@
 // tcgen05 PTX wrappers (every wait bounded), shared-memory descriptors.  Everything has internal linkage.
 #pragma once
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
+#include <utility>
 
 #include "knnconv_plan.cuh"
 
@@ -134,6 +136,21 @@ __device__ __forceinline__ void decode_item(const TcArgs& a, int item, int& n, i
 }  // namespace
 
 namespace fovi {
+// Launch with the programmatic-stream-serialization attribute (see the griddepcontrol note in the kernels):
+// the kernel may start while the previous kernel of the stream drains.  FOVI_B200_NO_PDL=1 launches plainly.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args&&... args) {
+  static const bool plain = getenv("FOVI_B200_NO_PDL") != nullptr;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = plain ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 // Tiled 3-D bf16 tensor map (box b0 x b1 x b2 of a tensor d0 x d1 x d2 with byte strides for d1, d2).
 int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
               uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128);
