@@ -55,6 +55,22 @@ def make_weights(geo):
             for i, (_, _, _, side) in enumerate(geo)]
 
 
+def sampler_algorithmic_bytes(grid_xy, fix_rc, H, W, size, C, in_bytes, out_bytes):
+    """Algorithmic bytes of the bilinear sampler per image x fixation: C * (U * in_bytes + N * out_bytes), U = distinct
+    in-image source pixels under the 2x2 footprints (computed here in float64; the count does not depend on the last bit).
+    fix_rc [M,2] normalised (row, col); square fixation windows of `size` pixels.  Returns (bytes, mean U)."""
+    total_u = 0
+    for r, c in fix_rc:
+        ix = grid_xy[:, 0] * (size / 2) + c * W - 0.5
+        iy = grid_xy[:, 1] * (size / 2) + r * H - 0.5
+        x0, y0 = np.floor(ix).astype(np.int64), np.floor(iy).astype(np.int64)
+        xx = np.concatenate([x0, x0 + 1, x0, x0 + 1]); yy = np.concatenate([y0, y0, y0 + 1, y0 + 1])
+        ok = (xx >= 0) & (xx < W) & (yy >= 0) & (yy < H)
+        total_u += np.unique(yy[ok] * W + xx[ok]).size
+    mean_u = total_u / len(fix_rc)
+    return C * (mean_u * in_bytes + grid_xy.shape[0] * out_bytes), mean_u
+
+
 def workload_name(args):
     return (f"sensor(a=1,N=4010,bilinear,zeros) x {args.fixations} fixations on {args.batch}x3x256x256 fp32 images "
             f"+ KNNConv stack 3-64-192-384-256-256 (K=121,25,9,9,9; bf16, fp32 accumulate)")
@@ -320,11 +336,9 @@ def main():
     n_dom = max(len(pair_layers), 1)
 
     if rank == 0:
-        from oracle import fovi_oracle as oracle
         fx = fix_host.numpy().reshape(-1, 2)[:64]
-        grid = retina.sampler.sampling_grid[0, 0].cpu().numpy()
-        samp_bytes, mean_u = oracle.sampler_footprint_bytes(grid, fx, np.full_like(fx, 256), 256, 256, 3, 4, 2)
-        samp_bytes_per = samp_bytes / fx.shape[0]
+        grid = retina.sampler.sampling_grid[0, 0].cpu().numpy().astype(np.float64)
+        samp_bytes_per, mean_u = sampler_algorithmic_bytes(grid, fx.astype(np.float64), 256, 256, 256, 3, 4, 2)
         sampler_gbs = samp_bytes_per * M / (per[0] * 1e-3) / 1e9
         value = world * M * args.steps / (ms_total * 1e-3)
         e2e = world * M * args.steps / (ms_e2e * 1e-3)
