@@ -48,6 +48,8 @@ def load_reference(root):
     import fovi.arch.knnvit as knnvit
     import fovi.sensing.coords as coords
     import fovi.sensing.retina as retina
+    import fovi.sensing.policies as policies
+    load_reference.policies = policies
     return knn, retina, coords, knnvit
 
 
@@ -222,6 +224,25 @@ def main():
         print(f"config4 patch-embed {tag}: Nin {int(t['n_in'])} tokens {o_ref.shape[-1]} K {pe._k} V {V} err {e:.2e}")
         save(f"config4_patch_embed_{tag}.npz", out_b2=o_ref, in_cartesian=pe.in_coords.cartesian.numpy(), out_cartesian=pe.out_coords.cartesian.numpy(),
              out_cortical=pe.out_coords.cortical.numpy(), **t)
+
+    # ------------------------------------------------------------ fixation policies (seeded NumPy global state)
+    pol = {}
+    rt = sensors["a1"]
+    rt.sampler.mode = "bilinear"
+    xb = synth_images(7, (3, 3, 256, 256))
+    for name, kw, train in (("near_eval", dict(norm_dist_from_center=0.25), False),
+                            ("near_train", dict(norm_dist_from_center=0.25, add_aspect_variation=True, nonrandom_first=True), True),
+                            ("crop_train", dict(add_aspect_variation=True), True)):
+        p_ref = load_reference.policies.MultiRandomSaccadePolicy(rt, n_fixations=4, **kw)
+        p_ref.train(train)
+        np.random.seed(11)
+        out = p_ref(torch.from_numpy(xb))
+        pol[f"{name}_fixations"] = out["fixations"].numpy()
+        pol[f"{name}_sizes"] = out["fixation_sizes"].numpy()
+        pol[f"{name}_x_fixs"] = out["x_fixs"].numpy()
+        pol[f"{name}_deltas"] = out["fix_deltas"].numpy()
+        pol[f"{name}_next_random"] = np.float64(np.random.uniform())          # the stream position after the call
+    save("policy_small.npz", **pol)
 
     # ------------------------------------------------------------ max pooling (next-row fixture)
     c = sensors["a0p5"].sampler.coords

@@ -129,3 +129,26 @@ def test_fused_sample_knnconv_call_equals_two_calls(golden):
     want = cplan.forward(xin, wt, relu=True, out_dtype=torch.float32, batch=B * F)
     cplan.check()
     assert y.shape == (B * F, 3975, 64) and torch.equal(y, want)
+
+
+@pytest.mark.parametrize("name,kw,train", [
+    ("near_eval", dict(norm_dist_from_center=0.25), False),
+    ("near_train", dict(norm_dist_from_center=0.25, add_aspect_variation=True, nonrandom_first=True), True),
+    ("crop_train", dict(add_aspect_variation=True), True),
+])
+def test_policy_forward_matches_reference(golden, name, kw, train):
+    """The batched policy (one sampler launch for all fixations) returns the reference policy's dictionary bit for bit."""
+    from fovi_b200.policies import MultiRandomSaccadePolicy
+    from fovi_b200.sensing import RetinalTransform
+    g = golden("policy_small.npz")
+    rt = RetinalTransform(resolution=64, start_res=256, fov=16, cmf_a=1.0, sampler="grid_bilinear", fixation_size=256, device="cuda")
+    pol = MultiRandomSaccadePolicy(rt, n_fixations=4, **kw)
+    pol.train(train)
+    x = torch.from_numpy(synth_images(7, (3, 3, 256, 256))).cuda()
+    np.random.seed(11)
+    out = pol(x)
+    assert np.array_equal(out["fixations"].cpu().numpy(), g[f"{name}_fixations"])
+    assert np.array_equal(out["fixation_sizes"].numpy(), g[f"{name}_sizes"])
+    assert np.array_equal(out["fix_deltas"].cpu().numpy(), g[f"{name}_deltas"])
+    assert out["x_fixs"].shape == (3, 4, 3, 4010)
+    assert np.array_equal(out["x_fixs"].cpu().numpy(), g[f"{name}_x_fixs"])

@@ -111,3 +111,27 @@ def test_all_gather_rows_two_gloo_ranks(n_rows):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_gloo_worker, args=(2, port, n_rows), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("name,kw,train", [
+    ("near_eval", dict(norm_dist_from_center=0.25), False),
+    ("near_train", dict(norm_dist_from_center=0.25, add_aspect_variation=True, nonrandom_first=True), True),
+    ("crop_train", dict(add_aspect_variation=True), True),
+])
+def test_policy_draws_reference_fixations(golden, name, kw, train):
+    """Seeded NumPy state -> the same fixation centres and window sizes as the reference policy, and the random stream
+    ends at the same position."""
+    import types
+    from fovi_b200.policies import MultiRandomSaccadePolicy
+    g = golden("policy_small.npz")
+    rt = types.SimpleNamespace(fixation_size=256, dtype=torch.float32, device="cpu")
+    pol = MultiRandomSaccadePolicy(rt, n_fixations=4, **kw)
+    pol.train(train)
+    np.random.seed(11)
+    fix, size = pol.draw((256, 256), 3, 4)
+    nxt = np.random.uniform()
+    if kw.get("nonrandom_first"):
+        fix[:, 0] = 0.5
+    assert np.array_equal(fix, g[f"{name}_fixations"])
+    assert np.array_equal(size, g[f"{name}_sizes"])
+    assert nxt == float(g[f"{name}_next_random"])
