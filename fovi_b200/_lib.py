@@ -26,6 +26,7 @@ SIGNATURES = {
     "fovi_knnconv_cin_packed": (C.c_int, [_P]),
     "fovi_knnconv_nnz": (C.c_int64, [_P]),
     "fovi_knnconv_x_layout": (C.c_int, [_P]),
+    "fovi_knnconv_tc_supported": (C.c_int, [_P]),
     "fovi_knnconv_pack_weights": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, _P]),
     "fovi_knnconv_packed_weight_bytes": (C.c_int64, [_P, C.c_int]),
     "fovi_pack_points": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P]),

@@ -244,6 +244,10 @@ extern "C" void fovi_knnconv_plan_destroy(fovi_knnconv_plan* p) {
 extern "C" int fovi_knnconv_cin_packed(const fovi_knnconv_plan* p) { return p ? p->cin_packed : -1; }
 extern "C" int64_t fovi_knnconv_nnz(const fovi_knnconv_plan* p) { return p ? p->nnz : -1; }
 extern "C" int fovi_knnconv_x_layout(const fovi_knnconv_plan* p) { return p ? p->x_layout : -1; }
+extern "C" int fovi_knnconv_tc_supported(const fovi_knnconv_plan* p) {
+  if (!p || !p->ct) return 0;
+  return (p->x_layout == FOVI_X_PAIRS ? p->sp : p->kp) <= 256 ? 1 : 0;
+}
 
 extern "C" int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* p, int dst_dtype) {
   if (!p || !fovi::valid_dtype(dst_dtype)) return -1;

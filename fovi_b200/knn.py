@@ -145,7 +145,8 @@ class KNNConvLayer(nn.Module):
             return self._forward(X_l)
 
     def _forward(self, X_l):
-        if self.precision == "fp32":
+        # shapes the tensor-core kernel does not cover (c_out not a multiple of 16, > 256 neighbours) run on the exact kernel
+        if self.precision == "fp32" or not self._plan.tc_supported:
             y = self._plan.forward_f32(X_l, self.packed_weight(torch.float32), self.bias)
             return y.to(X_l.dtype)
         out_dtype = torch.float32 if X_l.dtype == torch.float32 else torch.bfloat16

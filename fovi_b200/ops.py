@@ -106,6 +106,7 @@ class KnnConvPlan:
         self.cin_packed = lib.fovi_knnconv_cin_packed(h)
         self.nnz = lib.fovi_knnconv_nnz(h)
         self.x_layout = lib.fovi_knnconv_x_layout(h)
+        self.tc_supported = bool(lib.fovi_knnconv_tc_supported(h))
         self.n_pairs = (self.n_in + 1) // 2
 
     def __del__(self):

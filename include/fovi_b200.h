@@ -131,6 +131,9 @@ void fovi_knnconv_plan_destroy(fovi_knnconv_plan* plan);
 int fovi_knnconv_cin_packed(const fovi_knnconv_plan* plan);
 /* FOVI_X_BNC or FOVI_X_PAIRS (c_in <= 4). */
 int fovi_knnconv_x_layout(const fovi_knnconv_plan* plan);
+/* 1 if fovi_knnconv_forward (tensor cores) covers this plan's shape: c_out a multiple of 16 and neighbour lists of
+ * at most 256 entries; 0 otherwise (fovi_knnconv_forward_f32 covers every shape). */
+int fovi_knnconv_tc_supported(const fovi_knnconv_plan* plan);
 /* Number of non-pad (n,k) entries: algorithmic FLOPs per image = 2*c_in*c_out*nnz. */
 int64_t fovi_knnconv_nnz(const fovi_knnconv_plan* plan);
 

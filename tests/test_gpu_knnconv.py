@@ -166,3 +166,20 @@ def test_empty_batch(ops, golden):
     wt = plan.pack_weights(torch.zeros((384, 3 * int(g["V"])), device="cuda"))
     y = plan.forward(torch.empty((0, plan.n_pairs, 128, 8), dtype=torch.bfloat16, device="cuda"), wt, batch=0)
     assert y.shape == (0, plan.n_out, 384)
+
+
+def test_shapes_outside_the_tensor_core_path(ops):
+    """c_out that is not a multiple of 16: the tensor-core entry point refuses it before any launch, the exact kernel and the
+    module (which then uses the exact kernel) handle it."""
+    from fovi_b200._lib import FoviError
+    rs = np.random.RandomState(5)
+    B, Cin, Nin, Nout, K, V, Cout = 2, 3, 20, 7, 5, 9, 10
+    x = rs.standard_normal((B, Cin, Nin)).astype(f32)
+    idx = rs.randint(0, Nin + 1, (K, Nout)).astype(np.int32); tap = rs.randint(0, V, (Nout, K)).astype(np.uint16)
+    w = rs.standard_normal((Cout, Cin * V)).astype(f32)
+    plan = ops.KnnConvPlan(idx, tap, Nin, V, Cin, Cout)
+    assert not plan.tc_supported
+    with pytest.raises(FoviError, match="unsupported"):
+        plan.pack_weights(dev(w))
+    y = plan.forward_f32(dev(x), plan.pack_weights(dev(w), dtype=torch.float32)).cpu().numpy()
+    assert rel_max(y, oracle.knnconv_forward_closed_form(x, idx, tap.astype(np.int64), V, w)) < F32_TOL
