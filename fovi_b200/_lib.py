@@ -32,6 +32,7 @@ SIGNATURES = {
     "fovi_pack_points": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_forward": (C.c_int, [_P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knnconv_forward_f32": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_knnconv_selftest_wait_timeout": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_check": (C.c_int, [_P, _P]),
     "fovi_static_scratch_bytes": (C.c_int64, []),
     "fovi_knnconv_forward_bcn_static": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),

@@ -92,7 +92,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     uint32_t s = 0, ph = 0;
     uint32_t issued = 0;
     bool ok = true;
-    int item = blockIdx.x, buf = 0, cnt = 0;
+    int item = a.skip_loads ? a.total_items : blockIdx.x, buf = 0, cnt = 0;
     if (item < a.total_items) {  // first item's list straight into buffer 0
       int n, mt, ctile;
       decode_item(a, item, n, mt, ctile);
@@ -136,7 +136,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int st = 0; st < steps; ++st) {
           const uint32_t full = smem_u32(&hdr->full[s]);
           if (lane == 0) {
-            ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1);
+            ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit);
             if (ok) mbar_expect_tx(full, a.stage_bytes);
           }
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -162,7 +162,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           int k = 0, cc = 0;
           for (int st = 0; st < steps; ++st) {
             const uint32_t full = smem_u32(&hdr->full[s]);
-            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit)) { ok = false; break; }
             mbar_expect_tx(full, a.stage_bytes);
             const uint32_t sa = stages0 + s * a.stage_bytes;
             tma_load_3d(sa, &tmA, full, cc * 64, tb_idx[k], m0);
@@ -177,7 +177,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           int k = 0, cc = 0;
           for (int st = 0; st < steps; ++st) {
             const uint32_t full = smem_u32(&hdr->full[s]);
-            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit)) { ok = false; break; }
             mbar_expect_tx(full, a.stage_bytes);
             const uint32_t sa = stages0 + s * a.stage_bytes;
 #pragma unroll
@@ -230,11 +230,11 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int next = item + gridDim.x;
         const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;  // consumed next round
         const int steps = C64 ? cnt * chunks : (cnt * chunks + 7) / 8;
-        if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 2)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 2, a.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * a.acc_cols;
         for (int st = 0; st < steps; ++st) {
-          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, a.status, 3)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, a.status, 3, a.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = stages0 + s * a.stage_bytes, sb = sa + b_stage_off;
 #pragma unroll
@@ -274,7 +274,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       decode_item(a, item, n, mt, ctile);
       const int next = item + gridDim.x;
       const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;
-      ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4);
+      ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4, a.wait_limit);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave as a whole warp or not at all
       if (!ok) break;
       tc_fence_after();
@@ -372,8 +372,8 @@ int fovi::encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, u
   return FOVI_OK;
 }
 
-extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
-                                    int y_dtype, int B, int relu, void* stream) {
+static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype, int B,
+                                int relu, void* stream, int skip_loads, uint32_t wait_limit) {
   if (!p || B < 0 || !fovi::valid_dtype(y_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   if (B == 0) return FOVI_OK;  // an empty batch has no buffers to look at
   if (!X || !Wt || !Y) return FOVI_ERR_INVALID_ARGUMENT;
@@ -387,7 +387,7 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   // FOVI_B200_SINGLE_CTA=1 keeps the single-CTA kernel (for comparison runs).
   static const bool single_only = getenv("FOVI_B200_SINGLE_CTA") != nullptr;
   if (c64 && !single_only && B > BM && ct % 32 == 0) {
-    const int rc2 = fovi::launch_knnconv_tc_pair(p, X, Wt, bias, Y, y_dtype, B, relu, reinterpret_cast<cudaStream_t>(stream));
+    const int rc2 = fovi::launch_knnconv_tc_pair(p, X, Wt, bias, Y, y_dtype, B, relu, reinterpret_cast<cudaStream_t>(stream), skip_loads, wait_limit);
     if (rc2 != FOVI_ERR_UNSUPPORTED) return rc2;
   }
 
@@ -398,6 +398,7 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
   a.kp = pairs ? p->sp : p->kp; a.B = B; a.n_in = p->n_in; a.n_out = p->n_out; a.c_out = p->c_out; a.cp = cp;
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
+  a.wait_limit = wait_limit; a.skip_loads = skip_loads;
   const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
   if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;
@@ -446,6 +447,17 @@ extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const v
     FOVI_CUDA(fovi::launch_pdl(fovi_knnconv_tc_kernel<MODE_C8>, grid, 192, smem, st, tmA, tmB, a));
   }
   return fovi::after_launch("fovi_knnconv_tc_kernel");
+}
+
+extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
+                                    int y_dtype, int B, int relu, void* stream) {
+  return knnconv_forward_impl(p, X, Wt, bias, Y, y_dtype, B, relu, stream, 0, WAIT_LIMIT);
+}
+
+extern "C" int fovi_knnconv_selftest_wait_timeout(fovi_knnconv_plan* p, const void* X, const void* Wt, void* Y, int y_dtype, int B,
+                                                  void* stream) {
+  // the kernel's consumers wait for operands that never come; after 4096 attempts each wait gives up
+  return knnconv_forward_impl(p, X, Wt, nullptr, Y, y_dtype, B, 0, stream, 1, 4096u);
 }
 
 extern "C" int fovi_knnconv_check(fovi_knnconv_plan* p, void* stream) {

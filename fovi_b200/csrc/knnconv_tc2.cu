@@ -24,6 +24,7 @@ struct Tc2Args {
   int kp, B, n_in, n_out, c_out, cp;
   int ct, n_ct, n_mt2, nstage, relu, y_f32, total_items;
   uint32_t stage_bytes, table_bytes;
+  uint32_t wait_limit; int skip_loads;   // as in TcArgs
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -114,7 +115,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
     // ------------------------------------------------------------ producer (both CTAs)
     uint32_t s = 0, ph = 0;
     bool ok = true;
-    int item = pair, buf = 0, cnt = 0;
+    int item = a.skip_loads ? a.total_items : pair, buf = 0, cnt = 0;
     if (item < a.total_items) {
       int n, mt2, ctile;
       decode_item2(a, item, n, mt2, ctile);
@@ -152,7 +153,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         const int steps = cnt * chunks;
         int k = 0, cc = 0;
         for (int st = 0; st < steps; ++st) {
-          if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 11)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 11, a.wait_limit)) { ok = false; break; }
           const uint32_t full_leader = map_to_cta(smem_u32(&hdr->full[s]), 0);
           if (rank == 0) mbar_expect_tx(smem_u32(&hdr->full[s]), 2u * a.stage_bytes);   // both CTAs' bytes
           const uint32_t sa = stages0 + s * a.stage_bytes;
@@ -192,11 +193,11 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         const int next = item + n_pairs;
         const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;
         const int steps = cnt * chunks;
-        if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 12)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 12, a.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * 256u;
         for (int st = 0; st < steps; ++st) {
-          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, a.status, 13)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&hdr->full[s]), ph, abort_flag, a.status, 13, a.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = stages0 + s * a.stage_bytes, sb = sa + A_STAGE_BYTES;
 #pragma unroll
@@ -228,7 +229,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       decode_item2(a, item, n, mt2, ctile);
       const int next = item + n_pairs;
       const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;
-      ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 14);
+      ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 14, a.wait_limit);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -290,7 +291,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 }  // namespace
 
 int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype,
-                                 int B, int relu, cudaStream_t st) {
+                                 int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit) {
   const int ct = p->ct, cp = p->cin_packed;
   if (p->x_layout != FOVI_X_BNC || cp % 64 || !ct || ct % 32 || ct < 32 || B <= BM) return FOVI_ERR_UNSUPPORTED;
   const int sms = fovi::sm_count();
@@ -301,6 +302,7 @@ int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, cons
   a.kp = p->kp; a.B = B; a.n_in = p->n_in; a.n_out = p->n_out; a.c_out = p->c_out; a.cp = cp;
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt2 = (B + 2 * BM - 1) / (2 * BM);
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
+  a.wait_limit = wait_limit; a.skip_loads = skip_loads;
   const long long items = (long long)a.n_mt2 * p->n_out * a.n_ct;
   if (items >= (1ll << 31) || a.kp > 32 * TBQ) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;

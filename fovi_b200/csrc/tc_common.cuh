@@ -23,6 +23,8 @@ struct TcArgs {
   const float* bias; void* Y; int* status;
   int kp, B, n_in, n_out, c_out, cp;
   int ct, n_ct, n_mt, nstage, relu, y_f32, total_items;
+  uint32_t wait_limit;   // try_wait attempts before a wait gives up
+  int skip_loads;        // self-test: the producer withholds every operand load, so the first consumer wait must give up
   uint32_t acc_cols, tmem_cols;  // columns per accumulator (power of two >= ct) and allocated in total (two accumulators)
   const unsigned char* X; const unsigned char* Wt; const unsigned char* zero_block; int n_pairs;  // PAIRS mode
   uint32_t stage_bytes, table_bytes;
@@ -48,8 +50,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when it gave up or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          uint32_t limit = WAIT_LIMIT) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 255u && *abort_flag) return false;
   }
@@ -156,5 +159,5 @@ int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_
               uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128);
 // CTA-pair variant of the 64-channel mode (knnconv_tc2.cu).  Returns FOVI_ERR_UNSUPPORTED when it does not apply.
 int launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype,
-                           int B, int relu, cudaStream_t st);
+                           int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit);
 }  // namespace fovi

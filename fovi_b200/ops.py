@@ -172,6 +172,16 @@ class KnnConvPlan:
                                                _ptr(out), y_layout, B, int(relu), _stream()), "fovi_knnconv_forward_f32")
         return out
 
+    def selftest_wait_timeout(self, x_bnc, wt, batch=None, out_dtype=torch.bfloat16):
+        """Diagnostic: launch the tensor-core kernel with its operand loads withheld and a short wait limit.  The next
+        `check()` must raise FoviError (device timeout) and the context stays usable."""
+        _need_cuda(x_bnc, wt)
+        B = (x_bnc.shape[0] * 128 if batch is None else int(batch)) if self.x_layout == X_PAIRS else x_bnc.shape[0]
+        out = torch.zeros((B, self.n_out, self.c_out), dtype=out_dtype, device=x_bnc.device)
+        with torch.cuda.device(x_bnc.device):
+            check(lib.fovi_knnconv_selftest_wait_timeout(self._h, _ptr(x_bnc), _ptr(wt), _ptr(out), _dt(out.dtype), B, _stream()),
+                  "fovi_knnconv_selftest_wait_timeout")
+
     def check(self):
         """Synchronise the current stream and raise if a tensor-core launch gave up on a wait."""
         with torch.cuda.device(self.device):

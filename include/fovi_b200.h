@@ -190,6 +190,14 @@ int fovi_knnconv_forward_f32(const fovi_knnconv_plan* plan, const void* X, int x
                              const float* Wt, const float* bias, float* Y, int y_layout, int B, int relu,
                              void* stream);
 
+/* Diagnostic for the failure path: launches the plan's tensor-core kernel with every operand load withheld and a short
+ * wait limit, so the kernel's first consumer waits run out.  Nothing faults or hangs: the kernel records the wait site,
+ * all its roles leave, tensor memory is freed.  A following fovi_knnconv_check must return FOVI_ERR_DEVICE_TIMEOUT, and
+ * the context must remain usable (the next fovi_knnconv_forward gives correct results).  Y's contents are unspecified.
+ * The reference has no counterpart (it has no device-side waits). */
+int fovi_knnconv_selftest_wait_timeout(fovi_knnconv_plan* plan, const void* X, const void* Wt, void* Y, int y_dtype, int B,
+                                       void* stream);
+
 /* Synchronises `stream` and returns FOVI_ERR_DEVICE_TIMEOUT if any tensor-core launch on this
  * plan since the last check gave up on a wait; clears the word. */
 int fovi_knnconv_check(fovi_knnconv_plan* plan, void* stream);
