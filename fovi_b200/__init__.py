@@ -9,7 +9,7 @@ exists.
 import importlib
 
 __version__ = "0.1"
-_LAZY = ("ops", "sensing", "knn", "coords", "dist", "build", "_lib")
+_LAZY = ("ops", "sensing", "knn", "alexnet", "tables", "policies", "pipeline", "coords", "dist", "build", "_lib")
 
 
 def __getattr__(name):

@@ -90,13 +90,63 @@ def rel_err(a, b):
     return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
 
 
+ALEXNET_SHIPPED = dict(in_res=64, in_channels=3, features_per_layer=[96, 256, 384, 384, 256], stride_per_layer=[2, 1, 1, 1, 1],
+                       pool_after=[0, 1, 4], k_per_layer=[121, 25, 9, 9, 9], out_res=1, auto_match_cart_resources=1, fov=16.0, cmf_a=0.5,
+                       norm_type="force_batch", ref_frame_mult=2, sample_cortex=True)
+
+
+def seed_alexnet(model, seed):
+    """Deterministic parameters for a KNNAlexNet (reference or fovi_b200: same module names): Kaiming-normal conv
+    weights, and batch-norm affine parameters / running statistics away from their defaults."""
+    for i, block in enumerate(model.layers):
+        if not hasattr(block, "conv"):
+            continue
+        rs = np.random.RandomState(seed + i)
+        cout, fan = block.conv.weight.shape
+        block.conv.weight.data.copy_(torch.from_numpy((rs.standard_normal((cout, fan)) * np.sqrt(2.0 / fan)).astype(f32)))
+        block.norm.weight.data.copy_(torch.from_numpy((0.5 + rs.random_sample(cout)).astype(f32)))
+        block.norm.bias.data.copy_(torch.from_numpy((0.2 * rs.standard_normal(cout)).astype(f32)))
+        block.norm.running_mean.copy_(torch.from_numpy((0.1 * rs.standard_normal(cout)).astype(f32)))
+        block.norm.running_var.copy_(torch.from_numpy((0.5 + rs.random_sample(cout)).astype(f32)))
+    if getattr(model, "n_classes", None) is not None:
+        rs = np.random.RandomState(seed + 100)
+        w = model.classifier.weight
+        w.data.copy_(torch.from_numpy((rs.standard_normal(tuple(w.shape)) / np.sqrt(w.shape[1])).astype(f32)))
+        model.classifier.bias.data.copy_(torch.from_numpy((0.1 * rs.standard_normal(w.shape[0])).astype(f32)))
+
+
+def alexnet_fixture(save):
+    """The shipped foveated AlexNet (config/fovi_alexnet.yaml: base_lowres, a=0.5, 64x64 resources, batch norm) run by the
+    reference in evaluation mode on CPU, float32: per-block outputs of sample 0 and the logits."""
+    import fovi.arch.knnalexnet as ref_alex
+    torch.manual_seed(0)
+    net = ref_alex.KNNAlexNet(n_classes=10, device="cpu", **ALEXNET_SHIPPED)
+    seed_alexnet(net, 300)
+    net.eval()
+    n0 = net.layers[0].in_coords.shape[0]
+    x = (np.random.RandomState(21).standard_normal((3, 3, n0))).astype(f32)
+    out = {"x_seed": np.int64(21), "n_points": np.array([n0] + [L.out_coords.shape[0] for L in net.layers], np.int64)}
+    h = torch.from_numpy(x)
+    for i, L in enumerate(net.layers):
+        h = L(h)
+        out[f"layer{i}_out_b0"] = h[0].numpy()
+        out[f"layer{i}_sum"] = h.double().sum((1, 2)).numpy()
+    out["features"] = h.numpy()
+    out["logits"] = net.classifier(h.reshape(h.shape[0], -1)).numpy()
+    save("alexnet_shipped.npz", **out)
+    print("alexnet point counts", out["n_points"], "logits", out["logits"][0, :4])
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
+    ap.add_argument("--only", default=None, choices=[None, "alexnet"], help="regenerate one fixture group only")
     args = ap.parse_args()
     knn, retina, coords, knnvit = load_reference(args.reference)
     torch.set_grad_enabled(False)
     save = lambda name, **kw: np.savez_compressed(os.path.join(HERE, name), **kw)  # noqa: E731
+    if args.only == "alexnet":
+        return alexnet_fixture(save)
 
     # ------------------------------------------------------------ sensors (geometry fixtures)
     sensors = {}
@@ -261,6 +311,8 @@ def main():
     save("pool_a0p5.npz", knn_idx_pad=idxp, knn_idx=pool.knn_indices.numpy().astype(np.int32), out=p_ref, n_in=np.int64(len(ic)),
          n_out=np.int64(len(oc)), **extra)
     print("point counts a=0.5 chain:", len(ic), len(oc))
+
+    alexnet_fixture(save)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,79 @@
+"""GPU: the shipped foveated AlexNet (conv -> batch norm -> ReLU -> max pool blocks, average pooling, classifier) on the
+kernels against the outputs the reference model produced on CPU in float32 with the same parameters."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import ALEXNET_SHIPPED, seed_alexnet
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def net():
+    from fovi_b200.alexnet import KNNAlexNet
+    m = KNNAlexNet(n_classes=10, device="cuda", **ALEXNET_SHIPPED)
+    seed_alexnet(m, 300)
+    return m.eval()
+
+
+def test_point_counts_and_state_dict_names(net, golden):
+    g = golden("alexnet_shipped.npz")
+    counts = [net.layers[0].in_coords.shape[0]] + [L.out_coords.shape[0] for L in net.layers]
+    assert counts == list(g["n_points"])
+    names = set(net.state_dict().keys())
+    for i in range(5):
+        for leaf in ("conv.weight", "norm.weight", "norm.bias", "norm.running_mean", "norm.running_var", "norm.num_batches_tracked"):
+            assert f"layers.{i}.{leaf}" in names
+    assert {"classifier.weight", "classifier.bias"} <= names
+    assert not any("conv.bias" in n for n in names)          # the reference blocks build their convs without bias
+
+
+def test_blocks_and_logits_match_reference(net, golden):
+    g = golden("alexnet_shipped.npz")
+    x = np.random.RandomState(int(g["x_seed"])).standard_normal((3, 3, int(g["n_points"][0]))).astype(np.float32)
+    assert net.points_path
+    h = torch.from_numpy(x).cuda()
+    for i, L in enumerate(net.layers):          # block by block, each fed the previous block's own (bf16-rounded) output
+        h = L(h)
+        ref = g[f"layer{i}_out_b0"]
+        assert h.shape[1:] == ref.shape
+        assert rel_l2(h[0].float().cpu().numpy(), ref) < 2e-2, i     # bf16 activations through up to six stages
+    logits = net(torch.from_numpy(x).cuda()).float().cpu().numpy()
+    assert logits.shape == (3, 10)
+    assert rel_l2(logits, g["logits"]) < 2e-2
+    feats = net.forward_points(__import__("fovi_b200").ops.pack_points(torch.from_numpy(x).cuda(), net.layers[0].conv.plan), 3)
+    assert rel_l2(feats.permute(0, 2, 1).float().cpu().numpy(), g["features"]) < 2e-2
+
+
+def test_first_block_alone_is_within_the_single_layer_bar(net, golden):
+    g = golden("alexnet_shipped.npz")
+    x = np.random.RandomState(int(g["x_seed"])).standard_normal((3, 3, int(g["n_points"][0]))).astype(np.float32)
+    y = net.layers[0](torch.from_numpy(x).cuda())
+    assert rel_l2(y[0].cpu().numpy(), g["layer0_out_b0"]) < 1e-2
+
+
+def test_folded_operands_follow_parameter_updates(net):
+    b = net.layers[2]
+    wt0, bias0 = b.folded_operands()
+    assert b.folded_operands()[0] is wt0                      # cached
+    with torch.no_grad():
+        b.norm.running_var.mul_(4.0)
+    wt1, _ = b.folded_operands()
+    assert wt1 is not wt0
+    np.testing.assert_allclose(wt1.float().cpu().numpy(), 0.5 * wt0.float().cpu().numpy(), rtol=2e-2, atol=1e-6)
+    with torch.no_grad():
+        b.norm.running_var.div_(4.0)
+
+
+def test_training_mode_is_refused(net):
+    net.train()
+    try:
+        with pytest.raises(RuntimeError):
+            net(torch.zeros(1, 3, net.layers[0].in_coords.shape[0], device="cuda"))
+    finally:
+        net.eval()
