@@ -15,7 +15,7 @@ from . import ops
 from .coords import auto_match_num_coords, get_in_out_coords
 from .knn import KNNConvLayer, KNNPoolingLayer, get_knn_conv_layer
 
-__all__ = ["KNNBatchNorm", "get_norm", "KNNAlexNetBlock", "KNNAlexNet"]
+__all__ = ["KNNBatchNorm", "get_norm", "KNNAlexNetBlock", "KNNAlexNet", "FoveatedAlexNet"]
 
 
 class KNNBatchNorm(nn.BatchNorm1d):
@@ -201,3 +201,35 @@ class KNNAlexNet(nn.Module):
         if self.n_classes is not None:
             x = self.classifier(x.reshape(x.shape[0], -1))
         return x
+
+
+class FoveatedAlexNet(nn.Module):
+    """Images and fixations in, per-fixation or fixation-averaged network outputs out: the supervised forward pass of the
+    reference model (fovi/fovinet.py:251-294: fixate, flatten '(f b)', run the network, un-flatten to [B, F, D]) with its
+    mean over fixations (``saccades.fix_agg: mean``), without the projector head.
+
+    The sensor writes all fixations of all images straight into the first convolution's input layout in one launch."""
+
+    def __init__(self, retina, network):
+        super().__init__()
+        self.retina, self.network = retina, network
+
+    @torch.no_grad()
+    def forward(self, images, fix_loc, fixation_size=None, fix_agg=None):
+        """images [B,3,H,W], fix_loc [B,F,2] (row, col in [0,1]) -> [B, F, D]; with fix_agg='mean' -> [B, D].
+        D = n_classes, or C_out*N_out flattened channel-major when the network has no classifier."""
+        net = self.network
+        if not net.points_path:
+            raise RuntimeError("FoveatedAlexNet needs a network whose blocks all run on the tensor-core path")
+        B, F = images.shape[0], fix_loc.shape[1]
+        xp, rows = self.retina.forward_points(images, fix_loc, fixation_size, conv_plan=net.layers[0].conv.plan)
+        h = net.forward_points(xp, rows)                                  # [(f b), N_out, C_out]
+        h = h.permute(0, 2, 1).reshape(rows, -1).float()
+        if net.n_classes is not None:
+            h = net.classifier(h)
+        h = h.view(F, B, -1).permute(1, 0, 2)
+        if fix_agg is None:
+            return h
+        if fix_agg == "mean":
+            return h.mean(1)
+        raise NotImplementedError(f"fix_agg {fix_agg!r}: 'mean' or None")

@@ -77,3 +77,25 @@ def test_training_mode_is_refused(net):
             net(torch.zeros(1, 3, net.layers[0].in_coords.shape[0], device="cuda"))
     finally:
         net.eval()
+
+
+def test_foveated_alexnet_equals_sampler_then_network(net):
+    from conftest import synth_images
+    from fovi_b200.alexnet import FoveatedAlexNet
+    from fovi_b200.sensing import RetinalTransform
+    rt = RetinalTransform(resolution=64, start_res=256, fov=16, cmf_a=0.5, style="isotropic", sampler="grid_nn", fixation_size=256,
+                          auto_match_cart_resources=1, device="cuda")
+    assert len(rt.sampler.coords) == net.layers[0].in_coords.shape[0]
+    B, F = 3, 4
+    img = torch.from_numpy(synth_images(3, (B, 3, 256, 256))).cuda()
+    fix = torch.from_numpy((0.25 + 0.5 * np.random.RandomState(4).random_sample((B, F, 2))).astype(np.float32)).cuda()
+    model = FoveatedAlexNet(rt, net)
+    per_fix = model(img, fix)
+    assert per_fix.shape == (B, F, 10)
+    # the reference's order of operations: one sensor call per fixation, the network on the '(f b)' batch
+    x_fixs = torch.stack([rt(img, fix[:, f]) for f in range(F)], 1)                         # [B,F,3,N]
+    flat = x_fixs.permute(1, 0, 2, 3).reshape(F * B, 3, -1)
+    ref = net(flat).view(F, B, -1).permute(1, 0, 2)
+    # the fused route rounds the sensor output to bf16 exactly as pack_points does, so the two agree to rounding of the classifier
+    assert rel_l2(per_fix.cpu().numpy(), ref.float().cpu().numpy()) < 1e-3
+    np.testing.assert_allclose(model(img, fix, fix_agg="mean").cpu().numpy(), per_fix.mean(1).cpu().numpy(), rtol=1e-6, atol=1e-6)
