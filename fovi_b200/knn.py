@@ -20,7 +20,8 @@ class KNNPoolingLayer(nn.Module):
     """Pooling over the K nearest neighbours; counterpart of the reference layer (fovi/arch/knn.py:276-397) for
     the modes 'max', 'avg' and 'sum' ('gaussian' is not built).  forward(X [B,C,N_in]) -> [B,C,N_out]."""
 
-    def __init__(self, k, in_coords, out_coords, mode="max", device="cuda", sample_cortex=True, gauss_sigma=10, batch_size=None):
+    def __init__(self, k, in_coords, out_coords, mode="max", device="cuda", sample_cortex=True, gauss_sigma=10, batch_size=None,
+                 table_builder=None):
         super().__init__()
         if mode not in ops.POOL_MODES:
             raise NotImplementedError(f"pooling mode {mode!r}: 'max', 'avg' and 'sum' are built")
@@ -29,7 +30,7 @@ class KNNPoolingLayer(nn.Module):
         n_in = in_coords.shape[0]
         self.k = torch.minimum(torch.tensor(k), torch.tensor(n_in))
         self._k = int(self.k.item())
-        self.knn_indices, self.knn_distances, _, _ = tables.knn_table(in_coords, out_coords, self._k, sample_cortex, batch_size)
+        self.knn_indices, self.knn_distances, _, _ = tables.knn_table(in_coords, out_coords, self._k, sample_cortex, batch_size, builder=table_builder)
         self.knn_pad_token_val = n_in
         self.knn_indices_pad_mask = self.knn_indices >= n_in
         self.knn_indices_pad_token = tables.pad_token_table(self.knn_indices, n_in)
@@ -54,11 +55,12 @@ class KNNConvLayer(nn.Module):
 
     Args as the reference (knn.py:423-430); ``precision`` ('bf16' | 'fp32') is an addition.
     ``tables_override`` = dict(knn_indices [K,n_out] int64, tap [n_out,K], V, ref_coords?) skips the
-    table construction (used to run recorded tables).
+    table construction (used to run recorded tables).  ``table_builder`` ('torch' | 'native', default from
+    ``tables.default_builder()``) selects how the tables are built (see fovi_b200/tables.py).
     """
 
     def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True,
-                 bias=False, ref_frame_side_length=None, batch_size=None, precision="bf16", tables_override=None):
+                 bias=False, ref_frame_side_length=None, batch_size=None, precision="bf16", tables_override=None, table_builder=None):
         super().__init__()
         if precision not in ("bf16", "fp32"):
             raise ValueError("precision must be 'bf16' or 'fp32'")
@@ -70,9 +72,11 @@ class KNNConvLayer(nn.Module):
         self.k = torch.minimum(torch.tensor(k), torch.tensor(n_in))
         self._k = int(self.k.item())
         if tables_override is None:
-            self.knn_indices, self.knn_distances, pts, cart = tables.knn_table(in_coords, out_coords, self._k, sample_cortex, batch_size)
+            self.knn_indices, self.knn_distances, pts, cart = tables.knn_table(in_coords, out_coords, self._k, sample_cortex, batch_size,
+                                                                               builder=table_builder)
             self.ref_coords, self.ref_grid_size = tables.reference_frame(self._k, ref_frame_side_length, arch_flag, in_coords.dtype)
-            self.tap, self.knn_coords = tables.tap_table(self.knn_indices, pts, cart, out_coords, self.ref_coords, bool(sample_cortex))
+            self.tap, self.knn_coords = tables.tap_table(self.knn_indices, pts, cart, out_coords, self.ref_coords, bool(sample_cortex),
+                                                         builder=table_builder)
         else:
             self.knn_indices = torch.as_tensor(np.asarray(tables_override["knn_indices"]), dtype=torch.long)
             self.tap = torch.as_tensor(np.asarray(tables_override["tap"]).astype(np.int64))

@@ -215,6 +215,29 @@ int fovi_sample_knnconv_fused(const fovi_sampler_plan* sampler, fovi_knnconv_pla
                               int y_dtype, int relu, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Table construction on the host, with a reproducible rule for ties.
+ * Replaces the neighbour search _compute_euclidean_distances_batched + topk (fovi/arch/knn.py:101-152) and
+ * compute_local_rf (fovi/arch/knn.py:599-647).  The reference's float32 library calls rank the (frequent) exact and
+ * near ties of a ring-symmetric sensor differently from machine to machine; here distances are evaluated in double
+ * precision from the float32 coordinates with correctly rounded operations in a fixed order and ties go to the lower
+ * index, so the tables are a function of the coordinates alone.  All pointers are HOST memory; no device is needed.
+ * ------------------------------------------------------------------------------------------ */
+
+/* pts [n_pts,dim]: the layer's input points followed by its pad ring (cortical or visual-field coordinates);
+ * targets [n_out,dim]: the output points.  idx_out [K,n_out]: the K nearest points of each target, nearest first
+ * (order: distance, then index); dist_out [K,n_out] (may be NULL): their distances. */
+int fovi_knn_table_build(const float* pts, int n_pts, int dim, const float* targets, int n_out, int K, int32_t* idx_out,
+                         float* dist_out);
+
+/* knn_idx [K,n_out] indexes pts (pad ring included).  sample_cortex != 0: each neighbour is placed at (distance to the
+ * output point in `pts`/`out_pts` coordinates, direction in the visual field `pts_cart`/`out_cart` [.,2]); == 0: at its
+ * own coordinates (dim == 2).  The neighbourhood is min-max normalised to [-1,1]^2 and each neighbour takes the nearest
+ * node of the side x side reference frame (node order x-major, ties to the lower node).
+ * tap_out [n_out,K]; nb_out [K,n_out,2] (may be NULL): the normalised neighbour coordinates. */
+int fovi_tap_table_build(const int32_t* knn_idx, int K, int n_out, const float* pts, int n_pts, int dim, const float* pts_cart,
+                         const float* out_pts, const float* out_cart, int side, int sample_cortex, uint16_t* tap_out, float* nb_out);
+
+/* ------------------------------------------------------------------------------------------
  * KNN pooling.
  * Replaces KNNPoolingLayer.forward (fovi/arch/knn.py:345-394) for the modes 'max', 'avg', 'sum':
  * reduction over the K neighbours of each output point, pad neighbours (and NaN inputs) ignored.

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from conftest import synth_images, kaiming_weight
+from oracle import fovi_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 f32 = np.float32
@@ -152,3 +153,20 @@ def test_policy_forward_matches_reference(golden, name, kw, train):
     assert np.array_equal(out["fix_deltas"].cpu().numpy(), g[f"{name}_deltas"])
     assert out["x_fixs"].shape == (3, 4, 3, 4010)
     assert np.array_equal(out["x_fixs"].cpu().numpy(), g[f"{name}_x_fixs"])
+
+
+def test_layer_on_natively_built_tables_matches_oracle(golden):
+    """table_builder='native': the layer's own tables feed both the kernel and the oracle."""
+    from fovi_b200.coords import get_in_out_coords
+    from fovi_b200.knn import KNNConvLayer
+    ic, oc, _ = get_in_out_coords(20, 16, 1.0, 2, auto_match_cart_resources=0)
+    torch.manual_seed(0)
+    layer = KNNConvLayer(8, 32, 9, ic, oc, device="cuda", ref_frame_side_length=3, bias=True, table_builder="native")
+    ref_layer = KNNConvLayer(8, 32, 9, ic, oc, device="cuda", ref_frame_side_length=3, bias=True, table_builder="torch")
+    assert layer.knn_indices.shape == ref_layer.knn_indices.shape and layer.tap.shape == ref_layer.tap.shape
+    x = torch.randn(3, 8, ic.shape[0], device="cuda")
+    y = layer(x).cpu().numpy()
+    V = layer.ref_coords.shape[0]
+    ref = oracle.knnconv_forward(x.cpu().numpy(), layer.knn_indices_pad_token.numpy(), layer.tap.numpy(), V,
+                                 layer.weight.detach().cpu().numpy(), layer.bias.detach().cpu().numpy())
+    assert rel_l2(y, ref) < 1e-2
