@@ -1,0 +1,140 @@
+"""Backward pass of KNNConv on the forward tensor-core kernel.
+
+Both gradient contractions of ``out[b,o,n] = sum_k sum_c Xpad[b,c,idx[k,n]] * W[o, c*V + tap[n,k]]``
+(fovi/arch/knn.py:538-557; the reference gets them from autograd through its gather, one-hot matmul and linear) are
+themselves table-driven gather-GEMMs, so each runs as a forward launch of ``fovi_knnconv_forward`` on a derived plan:
+
+* input gradient — the transposed layer: "output" points are the layer's input points m, the neighbours of m are the
+  output points n that list m, each with the tap it was given; channels swap roles
+  (``dX[b,m,c] = sum_{(n,k): idx[k,n]=m} sum_o dY[b,n,o] * W[o, c*V + tap[n,k]]``).
+* weight gradient — the contraction runs over the batch, so the batch takes the place of the channels: rows are the
+  output channels o, "points" are the layer's output points n holding ``dY^T [o][n][b]``, the "taps" are the layer's input
+  points m holding ``X^T [m][c][b]`` in the packed-weight layout, and there is one "output point" per filter tap v whose
+  neighbour list is every (n, m) pair that uses v
+  (``dW[o,c,v] = sum_{(n,k): tap[n,k]=v} sum_b dY[b,n,o] * X[b,idx[k,n],c]``).  Lists longer than the kernel's limit are
+  split and the parts summed.
+
+Operands are bf16 with float32 accumulation, as under the reference's autocast training.
+"""
+import numpy as np
+import torch
+
+from . import ops
+
+__all__ = ["KnnConvGrad", "knnconv_autograd"]
+
+MAX_LIST = 256      # longest neighbour list the tensor-core kernel takes
+
+
+def _grouped(keys, n_groups, limit=None):
+    """Stable grouping of entry indices by key.  Returns (order, group id of each ordered entry, position inside its
+    group, number of groups, owner key of each group); groups longer than `limit` are split into consecutive parts."""
+    order = np.argsort(keys, kind="stable")
+    k = keys[order]
+    start = np.searchsorted(k, np.arange(n_groups))
+    pos = np.arange(k.size) - start[k]
+    if limit is None:
+        return order, k, pos, n_groups, np.arange(n_groups)
+    counts = np.bincount(k, minlength=n_groups)
+    parts = np.maximum(1, -(-counts // limit))
+    first = np.concatenate([[0], np.cumsum(parts)[:-1]])
+    gid = first[k] + pos // limit
+    owner = np.repeat(np.arange(n_groups), parts)
+    return order, gid, pos % limit, int(parts.sum()), owner
+
+
+class KnnConvGrad:
+    """Derived plans of one KNNConv layer's backward pass (built on first use, cached)."""
+
+    def __init__(self, knn_idx_pad, tap, n_in, V, c_in, c_out, device):
+        idx = np.asarray(knn_idx_pad).astype(np.int64)          # [K, n_out], pad == n_in
+        tp = np.asarray(tap).astype(np.int64)                   # [n_out, K]
+        self.n_in, self.V, self.c_in, self.c_out, self.device = int(n_in), int(V), int(c_in), int(c_out), device
+        self.K, self.n_out = idx.shape
+        ks, ns = np.nonzero(idx != n_in)
+        self._n, self._m, self._v = ns, idx[ks, ns], tp[ns, ks]
+        self._dx_plan = None
+        self._dw_plans = {}
+        self.c_in_pad = -(-self.c_in // 16) * 16
+
+    # ---- dX
+    def dx_plan(self):
+        if self._dx_plan is None:
+            if self.c_in % 16:
+                raise NotImplementedError("input gradient needs in_channels to be a multiple of 16 (a first layer's input needs none)")
+            order, gid, pos, _, _ = _grouped(self._m, self.n_in)
+            kt = max(8, int(pos.max()) + 1 if pos.size else 8)
+            if kt > MAX_LIST:
+                raise NotImplementedError(f"an input point feeds {kt} outputs; the kernel takes lists up to {MAX_LIST}")
+            idx_t = np.full((kt, self.n_in), self.n_out, np.int32)
+            tap_t = np.zeros((self.n_in, kt), np.uint16)
+            idx_t[pos, gid] = self._n[order]
+            tap_t[gid, pos] = self._v[order]
+            self._dx_plan = ops.KnnConvPlan(idx_t, tap_t, self.n_out, self.V, self.c_out, self.c_in, device=self.device)
+            if not self._dx_plan.tc_supported:
+                raise NotImplementedError("the transposed layer is outside the tensor-core kernel's shapes")
+        return self._dx_plan
+
+    def input_grad(self, gy_points, weight):
+        """gy_points [B, n_out, c_out] bf16 contiguous, weight [c_out, c_in*V] -> dX [B, n_in, c_in] bf16 (channels last)."""
+        plan = self.dx_plan()
+        w_t = weight.detach().reshape(self.c_out, self.c_in, self.V).permute(1, 0, 2).reshape(self.c_in, self.c_out * self.V)
+        return plan.forward(gy_points, plan.pack_weights(w_t.contiguous()), out_dtype=torch.bfloat16)
+
+    # ---- dW
+    def dw_plan(self, bp):
+        if bp not in self._dw_plans:
+            order, gid, pos, n_groups, owner = _grouped(self._v, self.V, MAX_LIST)
+            kw = max(8, int(pos.max()) + 1 if pos.size else 8)
+            idx_w = np.full((kw, n_groups), self.n_out, np.int32)
+            tap_w = np.zeros((n_groups, kw), np.uint16)
+            idx_w[pos, gid] = self._n[order]
+            tap_w[gid, pos] = self._m[order]
+            plan = ops.KnnConvPlan(idx_w, tap_w, self.n_out, self.n_in, bp, self.c_in_pad, device=self.device)
+            if not plan.tc_supported:
+                raise NotImplementedError("the weight-gradient contraction is outside the tensor-core kernel's shapes")
+            self._dw_plans[bp] = (plan, torch.from_numpy(owner).to(self.device))
+        return self._dw_plans[bp]
+
+    def weight_grad(self, gy, x):
+        """gy [B, c_out, n_out] and x [B, c_in, n_in] (any strides/dtype) -> dW [c_out, c_in*V] float32."""
+        B = gy.shape[0]
+        bp = -(-B // 64) * 64
+        plan, owner = self.dw_plan(bp)
+        gy_t = torch.zeros((self.c_out, self.n_out, bp), dtype=torch.bfloat16, device=gy.device)
+        gy_t[:, :, :B] = gy.permute(1, 2, 0)
+        x_t = torch.zeros((self.n_in, self.c_in_pad, bp), dtype=torch.bfloat16, device=x.device)
+        x_t[:, :self.c_in, :B] = x.permute(2, 1, 0)
+        parts = plan.forward(gy_t, x_t, out_dtype=torch.float32)                # [c_out, groups, c_in_pad]
+        dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
+        dw.index_add_(1, owner, parts)
+        return dw[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)
+
+
+class _KnnConvFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, layer):
+        ctx.layer = layer
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x, weight)
+        with torch.no_grad():
+            return layer._forward(x)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight = ctx.saved_tensors
+        g = ctx.layer.grad_plans
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gyp = gy.permute(0, 2, 1).to(torch.bfloat16).contiguous()
+            gx = g.input_grad(gyp, weight).permute(0, 2, 1).to(x.dtype)
+        if ctx.needs_input_grad[1]:
+            gw = g.weight_grad(gy, x).to(weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = gy.float().sum((0, 2))
+        return gx, gw, gb, None
+
+
+def knnconv_autograd(layer, x):
+    """layer(x) with gradients: forward on the layer's kernels, backward as described in this module."""
+    return _KnnConvFunction.apply(x, layer.weight, layer.bias, layer)

@@ -4,7 +4,8 @@ and of the patch embeddings built on it (fovi/arch/knnvit.py:17-98, 224-290) on 
 Same constructor signatures, parameter names/shapes (``weight [C_out, C_in*V]`` c-major/v-minor,
 ``bias [C_out]``: reference checkpoints load unchanged) and table attributes.  The forward pass runs the
 tensor-core kernel (bf16 operands, fp32 accumulation) or, with ``precision='fp32'``, the exact
-float32 kernel.  Inference only: the kernels implement no backward pass.
+float32 kernel.  With gradients enabled the bf16 path is differentiable (fovi_b200/grad.py: both gradient
+contractions run on the same kernel).
 """
 import numpy as np
 import torch
@@ -101,6 +102,7 @@ class KNNConvLayer(nn.Module):
         self._plan = ops.KnnConvPlan(self.knn_indices_pad_token.numpy().astype(np.int32), self.tap.numpy().astype(np.uint16),
                                      n_in, V, in_channels, out_channels, device=dev)
         self._packed = {}          # dtype -> (weight version, data_ptr, packed tensor)
+        self._grad = None
 
     # ---- tables in the reference's own representation, built on demand (can be hundreds of MB)
     @property
@@ -142,11 +144,22 @@ class KNNConvLayer(nn.Module):
     def forward(self, X_l):
         """X_l [B,C_in,N_in] -> [B,C_out,N_out] in X_l's dtype (knn.py:538-557); the result is a
         channels-last view."""
-        if torch.is_grad_enabled() and X_l.requires_grad:
-            raise RuntimeError("fovi_b200.KNNConvLayer implements the forward pass only: call it under torch.no_grad() "
-                               "(for training keep the reference layer)")
+        if torch.is_grad_enabled() and (X_l.requires_grad or self.weight.requires_grad or (self.bias is not None and self.bias.requires_grad)):
+            if self.precision != "bf16" or not self._plan.tc_supported:
+                raise RuntimeError("the backward pass is built for the bf16 tensor-core path: call this layer under torch.no_grad()")
+            from .grad import knnconv_autograd
+            return knnconv_autograd(self, X_l)
         with torch.no_grad():
             return self._forward(X_l)
+
+    @property
+    def grad_plans(self):
+        """Derived plans of the backward pass (fovi_b200/grad.py), built on first use."""
+        if self._grad is None:
+            from .grad import KnnConvGrad
+            self._grad = KnnConvGrad(self.knn_indices_pad_token.numpy(), self.tap.numpy(), self.in_coords.shape[0], self.ref_coords.shape[0],
+                                     self.in_channels, self.out_channels, torch.device(self.device))
+        return self._grad
 
     def _forward(self, X_l):
         # shapes the tensor-core kernel does not cover (c_out not a multiple of 16, > 256 neighbours) run on the exact kernel

@@ -229,6 +229,34 @@ def knnconv_forward_closed_form(X, knn_idx_pad, tap, V, weight, bias=None, relu=
     return np.ascontiguousarray(out.transpose(0, 2, 1)).astype(f32)
 
 
+def knnconv_backward(X, knn_idx_pad, tap, V, weight, grad_out, dtype=np.float64):
+    """Gradients of :func:`knnconv_forward_closed_form` (what autograd computes through the reference's
+    gather / one-hot matmul / linear, fovi/arch/knn.py:538-557) for an upstream gradient ``grad_out [B,Cout,Nout]``:
+
+        dX[b,c,m]      = sum over (n,k) with idx[k,n] == m of  sum_o grad_out[b,o,n] * W[o, c*V + tap[n,k]]
+        dW[o,c*V + v]  = sum over (n,k) with tap[n,k] == v, idx[k,n] != pad of  sum_b grad_out[b,o,n] * X[b,c,idx[k,n]]
+        dbias[o]       = sum_{b,n} grad_out[b,o,n]
+
+    Returns (dX [B,Cin,Nin], dW [Cout,Cin*V], dbias [Cout]) as float32, accumulated in ``dtype``."""
+    X = np.asarray(X, dtype)
+    G = np.asarray(grad_out, dtype)
+    B, Cin, Nin = X.shape
+    K, Nout = knn_idx_pad.shape
+    Cout = weight.shape[0]
+    Wv = np.asarray(weight, dtype).reshape(Cout, Cin, V)
+    Xp = np.concatenate([X, np.zeros((B, Cin, 1), dtype)], 2)
+    dXp = np.zeros((B, Cin, Nin + 1), dtype)
+    dW = np.zeros((Cout, Cin, V), dtype)
+    for k in range(K):
+        wk = Wv[:, :, tap[:, k]]                                          # [Cout,Cin,Nout]
+        contrib = np.einsum("bon,ocn->bcn", G, wk, optimize=True)         # [B,Cin,Nout] -> scattered to idx[k]
+        np.add.at(dXp, (slice(None), slice(None), knn_idx_pad[k]), contrib)
+        xk = Xp[:, :, knn_idx_pad[k]]                                     # [B,Cin,Nout], zero at pad neighbours
+        gw = np.einsum("bon,bcn->ocn", G, xk, optimize=True)              # [Cout,Cin,Nout] -> scattered to tap[:,k]
+        np.add.at(dW, (slice(None), slice(None), tap[:, k]), gw)
+    return (dXp[:, :, :Nin].astype(f32), dW.reshape(Cout, Cin * V).astype(f32), G.sum((0, 2)).astype(f32))
+
+
 def knnconv_stack(X, layers, relu_between=True):
     """A chain of KNNConv layers with ReLU between them (the conv->ReLU skeleton of
     fovi/arch/knnalexnet.py:109-127 without norm/pool).  ``layers`` is a list of dicts

@@ -137,16 +137,45 @@ def alexnet_fixture(save):
     print("alexnet point counts", out["n_points"], "logits", out["logits"][0, :4])
 
 
+def backward_fixture(save, knn):
+    """Gradients of the reference KNNConvLayer from its own autograd (CPU, float32) on a small layer, and the oracle's
+    backward pinned to them."""
+    ic, oc, _ = knn.get_in_out_coords(24, 16, 1.0, 2, style="isotropic", auto_match_cart_resources=0, device="cpu")
+    torch.manual_seed(5)
+    layer = knn.KNNConvLayer(16, 32, 9, ic, oc, device="cpu", ref_frame_side_length=4, bias=True)
+    rs = np.random.RandomState(31)
+    V = layer.ref_coords.shape[0]
+    w = kaiming_weight(rs, 32, 16, V)
+    b = (0.1 * rs.standard_normal(32)).astype(f32)
+    x = rs.standard_normal((5, 16, len(ic))).astype(f32)
+    g = rs.standard_normal((5, 32, len(oc))).astype(f32)
+    with torch.enable_grad():
+        layer.weight.data.copy_(torch.from_numpy(w))
+        layer.bias.data.copy_(torch.from_numpy(b))
+        xt = torch.from_numpy(x).requires_grad_(True)
+        y = layer(xt)
+        y.backward(torch.from_numpy(g))
+    t = layer_tables(layer)
+    dX, dW, db = oracle.knnconv_backward(x, t["knn_idx_pad"], t["tap"].astype(np.int64), int(t["V"]), w, g)
+    for name, a, r in (("dX", dX, xt.grad.numpy()), ("dW", dW, layer.weight.grad.numpy()), ("dbias", db, layer.bias.grad.numpy())):
+        assert rel_err(a, r) < 1e-5, (name, rel_err(a, r))
+    save("backward_small.npz", y=y.detach().numpy(), dX=xt.grad.numpy(), dW=layer.weight.grad.numpy(), dbias=layer.bias.grad.numpy(),
+         seed=np.int64(31), **t)
+    print("backward fixture: n_in", len(ic), "n_out", len(oc), "V", V)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
-    ap.add_argument("--only", default=None, choices=[None, "alexnet"], help="regenerate one fixture group only")
+    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward"], help="regenerate one fixture group only")
     args = ap.parse_args()
     knn, retina, coords, knnvit = load_reference(args.reference)
     torch.set_grad_enabled(False)
     save = lambda name, **kw: np.savez_compressed(os.path.join(HERE, name), **kw)  # noqa: E731
     if args.only == "alexnet":
         return alexnet_fixture(save)
+    if args.only == "backward":
+        return backward_fixture(save, knn)
 
     # ------------------------------------------------------------ sensors (geometry fixtures)
     sensors = {}
@@ -313,6 +342,7 @@ def main():
     print("point counts a=0.5 chain:", len(ic), len(oc))
 
     alexnet_fixture(save)
+    backward_fixture(save, knn)
 
 
 if __name__ == "__main__":

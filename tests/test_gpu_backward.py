@@ -1,0 +1,110 @@
+"""GPU: gradients of KNNConvLayer (both contractions run on the forward tensor-core kernel) against the gradients the
+reference's autograd produced on CPU in float32 (tests/golden/backward_small.npz) and against the oracle's backward."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import kaiming_weight
+from oracle import fovi_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2          # relative L2, bf16 operands with float32 accumulation vs float32 reference
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+class _Pts:
+    def __init__(self, n):
+        self.shape = (n, 2)
+        self.dtype = torch.float32
+
+
+def _layer(g, c_in, c_out, bias=True):
+    from fovi_b200.knn import KNNConvLayer
+    n_in = int(g["n_in"])
+    return KNNConvLayer(c_in, c_out, g["knn_idx"].shape[0], _Pts(n_in), _Pts(g["knn_idx"].shape[1]), device="cuda", bias=bias,
+                        tables_override=dict(knn_indices=g["knn_idx"], tap=g["tap"], V=int(g["V"])))
+
+
+def test_gradients_match_reference_autograd(golden):
+    g = golden("backward_small.npz")
+    V, n_in = int(g["V"]), int(g["n_in"])
+    rs = np.random.RandomState(int(g["seed"]))
+    w = kaiming_weight(rs, 32, 16, V)
+    b = (0.1 * rs.standard_normal(32)).astype(np.float32)
+    x = rs.standard_normal((5, 16, n_in)).astype(np.float32)
+    gy = rs.standard_normal((5, 32, g["knn_idx"].shape[1])).astype(np.float32)
+    layer = _layer(g, 16, 32)
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(w))
+        layer.bias.copy_(torch.from_numpy(b))
+    xt = torch.from_numpy(x).cuda().requires_grad_(True)
+    y = layer(xt)
+    assert y.requires_grad and rel_l2(y.detach().cpu().numpy(), g["y"]) < TOL
+    y.backward(torch.from_numpy(gy).cuda())
+    layer.plan.check()
+    assert rel_l2(xt.grad.cpu().numpy(), g["dX"]) < TOL
+    assert rel_l2(layer.weight.grad.cpu().numpy(), g["dW"]) < TOL
+    assert rel_l2(layer.bias.grad.cpu().numpy(), g["dbias"]) < 1e-5
+    assert layer.weight.grad.shape == layer.weight.shape and xt.grad.shape == xt.shape
+
+
+def test_first_layer_weight_gradient_and_split_lists(golden):
+    """A 3-channel first layer (pair-layout forward): its input needs no gradient; with K=49 neighbours per output and 49
+    taps every tap's pair list is longer than the kernel's limit and is split."""
+    g = golden("config1.npz")
+    V, n_in = int(g["V"]), int(g["n_in"])
+    n_out = g["knn_idx_pad"].shape[1]
+    rs = np.random.RandomState(3)
+    w = kaiming_weight(rs, 64, 3, V)
+    x = rs.standard_normal((70, 3, n_in)).astype(np.float32)          # 70 rows: the batch is padded to 128 for the contraction
+    gy = rs.standard_normal((70, 64, n_out)).astype(np.float32)
+    from fovi_b200.knn import KNNConvLayer
+    layer = KNNConvLayer(3, 64, 49, _Pts(n_in), _Pts(n_out), device="cuda",
+                         tables_override=dict(knn_indices=g["knn_idx"], tap=g["tap"], V=V))
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(w))
+    y = layer(torch.from_numpy(x).cuda())
+    y.backward(torch.from_numpy(gy).cuda())
+    _, dW, _ = oracle.knnconv_backward(x[:8], g["knn_idx_pad"], g["tap"].astype(np.int64), V, w, gy[:8])
+    # the oracle on 8 rows is the check of a second, smaller run (the full batch would take minutes in NumPy)
+    layer.weight.grad = None
+    y8 = layer(torch.from_numpy(x[:8]).cuda())
+    y8.backward(torch.from_numpy(gy[:8]).cuda())
+    assert rel_l2(layer.weight.grad.cpu().numpy(), dW) < TOL
+    assert layer.grad_plans.dw_plan(64)[0].n_out > V                # lists were split
+    with pytest.raises(NotImplementedError):
+        xt = torch.from_numpy(x[:8]).cuda().requires_grad_(True)
+        layer(xt).sum().backward()
+
+
+def test_optimizer_steps_reduce_a_regression_loss(golden):
+    g = golden("backward_small.npz")
+    n_in, n_out = int(g["n_in"]), g["knn_idx"].shape[1]
+    torch.manual_seed(0)
+    layer = _layer(g, 16, 32)
+    teacher = _layer(g, 16, 32)
+    x = torch.randn(64, 16, n_in, device="cuda")
+    with torch.no_grad():
+        target = teacher(x).float()
+    opt = torch.optim.Adam(layer.parameters(), lr=0.01)
+    losses = []
+    for _ in range(20):
+        opt.zero_grad()
+        loss = ((layer(x).float() - target) ** 2).mean()
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < 0.7 * losses[0], losses
+    assert y_is_fresh(layer, x)
+
+
+def y_is_fresh(layer, x):
+    """The packed copy of the weights follows the optimizer's in-place updates."""
+    with torch.no_grad():
+        a = layer(x)
+        layer.refresh_weights()
+        b = layer(x)
+    return torch.equal(a, b)

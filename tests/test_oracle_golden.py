@@ -133,3 +133,17 @@ def test_pool_avg_sum(golden):
     x = synth_images(5, (2, 4, int(g["n_in"]))) - f32(0.5)
     np.testing.assert_allclose(oracle.knn_pool_avg(x, g["knn_idx_pad"]), g["out_avg"], rtol=1e-6, atol=1e-7)
     np.testing.assert_allclose(oracle.knn_pool_sum(x, g["knn_idx_pad"]), g["out_sum"], rtol=1e-6, atol=1e-7)
+
+
+def test_oracle_backward_matches_reference_autograd(golden):
+    g = golden("backward_small.npz")
+    V, n_in = int(g["V"]), int(g["n_in"])
+    rs = np.random.RandomState(int(g["seed"]))
+    from conftest import kaiming_weight
+    w = kaiming_weight(rs, 32, 16, V)
+    rs.standard_normal(32)                                   # the bias draw of the generator
+    x = rs.standard_normal((5, 16, n_in)).astype(np.float32)
+    gy = rs.standard_normal((5, 32, g["knn_idx"].shape[1])).astype(np.float32)
+    dX, dW, db = oracle.knnconv_backward(x, g["knn_idx_pad"], g["tap"].astype(np.int64), V, w, gy)
+    for a, r in ((dX, g["dX"]), (dW, g["dW"]), (db, g["dbias"])):
+        assert np.abs(a - r).max() <= 1e-5 * np.abs(r).max()
