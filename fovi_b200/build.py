@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfovi_b200.so")
-SOURCES = ["capi.cu", "sampler.cu", "knnconv.cu", "knnconv_tc.cu", "knnconv_tc2.cu", "knnpool.cu", "fused.cu", "tables.cu"]
+SOURCES = ["capi.cu", "sampler.cu", "knnconv.cu", "knnconv_tc.cu", "knnconv_tc2.cu", "knnpool.cu", "fused.cu", "tables.cu", "grad.cu", "depthwise.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 

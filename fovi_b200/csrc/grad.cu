@@ -1,0 +1,51 @@
+// Layout change used by the weight-gradient contraction of KNNConv: the batch index becomes the innermost
+// (contiguous) one, so that it can play the role of the channels in the tensor-core kernel.
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace {
+
+// src: logical [B, I, J], element (b,i,j) at b*sb + i*si + j*sj, with si == 1 (FAST_I) or sj == 1 (!FAST_I).
+// dst: [I, Jp, Bp] bf16, zero where j >= J or b >= B.  32x32 tiles of (batch, fast index) go through shared memory:
+// reads run along the source's contiguous index, writes along the batch.
+template <typename T, bool FAST_I>
+__global__ void batch_to_inner_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst, int B, int I, int J, int Jp, int Bp,
+                                      long long sb, long long si, long long sj) {
+  __shared__ float tile[32][33];
+  const int b0 = blockIdx.x * 32, f0 = blockIdx.y * 32, slow = blockIdx.z;
+  const int F = FAST_I ? I : J;   // extent of the fast index in the source
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int b = b0 + r, f = f0 + threadIdx.x;
+    const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
+    tile[r][threadIdx.x] = (b < B && f < F && j < J) ? ld_as_float(src + b * sb + i * si + j * sj) : 0.f;
+  }
+  __syncthreads();
+  const int Fd = FAST_I ? I : Jp;  // extent of the fast index in the destination
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int f = f0 + r, b = b0 + threadIdx.x;
+    if (f < Fd && b < Bp) {
+      const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
+      dst[((long long)i * Jp + j) * Bp + b] = __float2bfloat16_rn(tile[threadIdx.x][r]);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst,
+                                   int Jp, int Bp, void* stream) {
+  if (!fovi::valid_dtype(dtype) || B < 0 || I <= 0 || J <= 0 || Jp < J || Bp < B || Bp <= 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if (!src || !dst) return FOVI_ERR_INVALID_ARGUMENT;
+  if (si != 1 && sj != 1) return FOVI_ERR_UNSUPPORTED;
+  const bool fast_i = si == 1 && !(sj == 1 && J >= I);
+  const int fast = fast_i ? I : Jp, slow = fast_i ? Jp : I;
+  if (slow > 65535 || (fast + 31) / 32 > 65535) return FOVI_ERR_UNSUPPORTED;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid((Bp + 31) / 32, (fast + 31) / 32, slow), block(32, 8);
+#define RUN(T, FI) batch_to_inner_kernel<T, FI><<<grid, block, 0, st>>>((const T*)src, (__nv_bfloat16*)dst, B, I, J, Jp, Bp, sb, si, sj)
+  if (dtype == FOVI_F32) { if (fast_i) RUN(float, true); else RUN(float, false); }
+  else { if (fast_i) RUN(__nv_bfloat16, true); else RUN(__nv_bfloat16, false); }
+#undef RUN
+  return fovi::after_launch("batch_to_inner_kernel");
+}

@@ -84,7 +84,9 @@ class KnnConvGrad:
     # ---- dW
     def dw_plan(self, bp):
         if bp not in self._dw_plans:
-            order, gid, pos, n_groups, owner = _grouped(self._v, self.V, MAX_LIST)
+            # Lists are cut so that there are a few hundred of them (several per SM pair), whatever the number of taps.
+            limit = int(min(MAX_LIST, max(8, -(-self._v.size // 300 // 8) * 8)))
+            order, gid, pos, n_groups, owner = _grouped(self._v, self.V, limit)
             kw = max(8, int(pos.max()) + 1 if pos.size else 8)
             idx_w = np.full((kw, n_groups), self.n_out, np.int32)
             tap_w = np.zeros((n_groups, kw), np.uint16)
@@ -101,10 +103,8 @@ class KnnConvGrad:
         B = gy.shape[0]
         bp = -(-B // 64) * 64
         plan, owner = self.dw_plan(bp)
-        gy_t = torch.zeros((self.c_out, self.n_out, bp), dtype=torch.bfloat16, device=gy.device)
-        gy_t[:, :, :B] = gy.permute(1, 2, 0)
-        x_t = torch.zeros((self.n_in, self.c_in_pad, bp), dtype=torch.bfloat16, device=x.device)
-        x_t[:, :self.c_in, :B] = x.permute(2, 1, 0)
+        gy_t = ops.batch_to_inner(gy, bp=bp)                                           # [c_out, n_out, bp]
+        x_t = ops.batch_to_inner(x.permute(0, 2, 1), jp=self.c_in_pad, bp=bp)          # [n_in, c_in_pad, bp]
         parts = plan.forward(gy_t, x_t, out_dtype=torch.float32)                # [c_out, groups, c_in_pad]
         dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
         dw.index_add_(1, owner, parts)

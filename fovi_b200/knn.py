@@ -14,7 +14,7 @@ import torch.nn as nn
 from . import ops, tables
 from .coords import SamplingCoords, get_in_out_coords  # noqa: F401  (re-exported for callers of the reference API)
 
-__all__ = ["KNNPoolingLayer", "KNNConvLayer", "KNNPatchEmbedding", "KNNPartitioningPatchEmbedding", "KNNConvStack", "KNN_CONV_REGISTRY", "get_knn_conv_layer"]
+__all__ = ["KNNPoolingLayer", "KNNConvLayer", "KNNDepthwiseConvLayer", "KNNDepthwiseSeparableConvLayer", "KNNPatchEmbedding", "KNNPartitioningPatchEmbedding", "KNNConvStack", "KNN_CONV_REGISTRY", "get_knn_conv_layer"]
 
 
 class KNNPoolingLayer(nn.Module):
@@ -145,10 +145,11 @@ class KNNConvLayer(nn.Module):
         """X_l [B,C_in,N_in] -> [B,C_out,N_out] in X_l's dtype (knn.py:538-557); the result is a
         channels-last view."""
         if torch.is_grad_enabled() and (X_l.requires_grad or self.weight.requires_grad or (self.bias is not None and self.bias.requires_grad)):
-            if self.precision != "bf16" or not self._plan.tc_supported:
+            if self.precision == "bf16" and self._plan.tc_supported:
+                from .grad import knnconv_autograd
+                return knnconv_autograd(self, X_l)
+            if X_l.requires_grad:
                 raise RuntimeError("the backward pass is built for the bf16 tensor-core path: call this layer under torch.no_grad()")
-            from .grad import knnconv_autograd
-            return knnconv_autograd(self, X_l)
         with torch.no_grad():
             return self._forward(X_l)
 
@@ -191,6 +192,75 @@ class KNNConvLayer(nn.Module):
     def __repr__(self):
         return (f"{self.__class__.__name__}(\n\tin_channels={self.in_channels}\n\tout_channels={self.out_channels}\n\tk={self.k}\n\t"
                 f"n_ref={self.ref_coords.shape[0]}\n\tin_coords={self.in_coords}\n\tout_coords={self.out_coords}\n\tsample_cortex={self.sample_cortex}\n)")
+
+
+class _DepthwiseBase(KNNConvLayer):
+    """Shared part of the depthwise layers: the filter ``[C_in, V, g]`` in the kernel's ``[V, C_in*g]`` float32 layout."""
+
+    def _packed_depthwise(self, w):
+        key = (w._version, w.data_ptr())
+        hit = self._packed.get("dw")
+        if hit is None or hit[0] != key:
+            V = self.ref_coords.shape[0]
+            self._packed["dw"] = (key, w.detach().float().permute(1, 0, 2).reshape(V, self.out_channels).contiguous())
+        return self._packed["dw"][1]
+
+    def _check_no_grad(self, *tensors):
+        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+            raise RuntimeError("the depthwise layers implement the forward pass only: call them under torch.no_grad()")
+
+
+class KNNDepthwiseConvLayer(_DepthwiseBase):
+    """Depthwise KNN convolution: every input channel is filtered on its own into g = out/in output channels
+    (fovi/arch/knn.py:803-872).  Parameters as the reference: ``weight [C_in, V, g]``, ``bias [C_out]`` (a zero tensor
+    when bias=False).  forward(X [B,C_in,N_in]) -> [B,C_out,N_out]."""
+
+    def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True, bias=False,
+                 batch_size=None, ref_frame_side_length=None, **kwargs):
+        assert out_channels % in_channels == 0, "out_channels must be divisible by in_channels for depthwise conv"
+        super().__init__(in_channels, out_channels, k, in_coords, out_coords, device, arch_flag, sample_cortex, bias, ref_frame_side_length,
+                         batch_size, **kwargs)
+        dev = torch.device(device)
+        self.weight = nn.Parameter(torch.empty(in_channels, self.ref_coords.shape[0], out_channels // in_channels, device=dev))
+        if bias:
+            self.bias = nn.Parameter(torch.zeros(out_channels, device=dev))
+        else:
+            self.bias = None
+            self.zero_bias = torch.zeros(out_channels, device=dev)
+        bound = 1 / (in_channels * self._k)
+        nn.init.uniform_(self.weight, a=-bound, b=bound)
+
+    def forward(self, X_l):
+        self._check_no_grad(X_l, self.weight, self.bias)
+        with torch.no_grad():
+            return self._plan.depthwise(X_l, self._packed_depthwise(self.weight), self.bias)
+
+
+class KNNDepthwiseSeparableConvLayer(_DepthwiseBase):
+    """Depthwise KNN convolution followed by a pointwise linear map over channels (fovi/arch/knn.py:722-800).
+    Parameters as the reference: ``dw_conv [C_in, V, g]``, ``p_conv`` = Linear(C_out, C_out); the base class's dense
+    ``weight`` is kept (unused, as in the reference) so that state dicts line up.  The pointwise map is a plain dense
+    matrix product on the channels-last depthwise output and is left to the library GEMM."""
+
+    def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True, bias=False,
+                 batch_size=None, ref_frame_side_length=None, **kwargs):
+        assert out_channels % in_channels == 0, "out_channels must be divisible by in_channels for depthwise conv"
+        super().__init__(in_channels, out_channels, k, in_coords, out_coords, device, arch_flag, sample_cortex, bias, ref_frame_side_length,
+                         batch_size, **kwargs)
+        dev = torch.device(device)
+        self.dw_conv = nn.Parameter(torch.empty(in_channels, self.ref_coords.shape[0], out_channels // in_channels, device=dev))
+        self.p_conv = nn.Linear(out_channels, out_channels, bias=bias, device=dev)
+        bound = 1 / (in_channels * self._k)
+        nn.init.uniform_(self.dw_conv, a=-bound, b=bound)
+        nn.init.uniform_(self.p_conv.weight, a=-bound, b=bound)
+        if self.p_conv.bias is not None:
+            nn.init.zeros_(self.p_conv.bias)
+
+    def forward(self, X_l):
+        self._check_no_grad(X_l, self.dw_conv, self.p_conv.weight)
+        with torch.no_grad():
+            dw = self._plan.depthwise(X_l, self._packed_depthwise(self.dw_conv), None, y_layout=ops.ACT_BNC)     # [B, N_out, C_out]
+            return self.p_conv(dw).transpose(1, 2)
 
 
 class KNNPatchEmbedding(KNNConvLayer):
@@ -276,7 +346,7 @@ class KNNConvStack(nn.Module):
         return self.forward_points(xp, X.shape[0], out_dtype).permute(0, 2, 1)
 
 
-KNN_CONV_REGISTRY = {"default": KNNConvLayer, "b200": KNNConvLayer}
+KNN_CONV_REGISTRY = {"default": KNNConvLayer, "b200": KNNConvLayer, "dwsep": KNNDepthwiseSeparableConvLayer, "dw": KNNDepthwiseConvLayer}
 
 
 def get_knn_conv_layer(name):

@@ -182,6 +182,24 @@ class KnnConvPlan:
             check(lib.fovi_knnconv_selftest_wait_timeout(self._h, _ptr(x_bnc), _ptr(wt), _ptr(out), _dt(out.dtype), B, _stream()),
                   "fovi_knnconv_selftest_wait_timeout")
 
+    def depthwise(self, x, wp, bias=None, relu=False, x_layout=ACT_BCN, y_layout=ACT_BCN, out_dtype=None):
+        """Depthwise convolution on this plan's tables.  x [B,c_in,n_in] (BCN) or [B,n_in,c_in] (BNC), float32/bf16;
+        wp float32 [V, c_out] with wp[v, c*g+j] = W[c, v, j]."""
+        _need_cuda(x, wp, bias)
+        x = x.contiguous()
+        B = x.shape[0]
+        assert x.shape[1:] == ((self.c_in, self.n_in) if x_layout == ACT_BCN else (self.n_in, self.c_in)), x.shape
+        assert wp.dtype == torch.float32 and wp.shape == (self.V, self.c_out) and wp.is_contiguous()
+        if bias is not None:
+            bias = bias.detach().to(torch.float32).contiguous()
+        out_dtype = x.dtype if out_dtype is None else out_dtype
+        shape = (B, self.c_out, self.n_out) if y_layout == ACT_BCN else (B, self.n_out, self.c_out)
+        out = torch.empty(shape, dtype=out_dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib.fovi_knn_depthwise_forward(self._h, _ptr(x), _dt(x.dtype), x_layout, _ptr(wp), _ptr(bias) if bias is not None else None,
+                                                 _ptr(out), _dt(out.dtype), y_layout, B, int(relu), _stream()), "fovi_knn_depthwise_forward")
+        return out
+
     def check(self):
         """Synchronise the current stream and raise if a tensor-core launch gave up on a wait."""
         with torch.cuda.device(self.device):
@@ -259,6 +277,24 @@ def pack_points(x, cp=8, x_layout=X_BNC):
     with torch.cuda.device(x.device):
         check(lib.fovi_pack_points(_ptr(x), _dt(x.dtype), B, Cc, N, _ptr(dst), cp, x_layout, _stream()), "fovi_pack_points")
     return dst
+
+
+def batch_to_inner(src, jp=None, bp=None, out=None):
+    """src: logical [B, I, J] float32/bf16 CUDA tensor of any strides with one of the last two contiguous
+    -> [I, jp, bp] bf16 with the batch innermost, zero-padded (jp >= J, bp >= B)."""
+    _need_cuda(src)
+    B, I, J = src.shape
+    jp, bp = J if jp is None else int(jp), B if bp is None else int(bp)
+    sb, si, sj = src.stride()
+    if si != 1 and sj != 1:
+        src = src.contiguous()
+        sb, si, sj = src.stride()
+    if out is None:
+        out = torch.empty((I, jp, bp), dtype=torch.bfloat16, device=src.device)
+    assert out.shape == (I, jp, bp) and out.dtype == torch.bfloat16 and out.is_contiguous()
+    with torch.cuda.device(src.device):
+        check(lib.fovi_batch_to_inner(_ptr(src), _dt(src.dtype), B, I, J, sb, si, sj, _ptr(out), jp, bp, _stream()), "fovi_batch_to_inner")
+    return out
 
 
 def launch_count():

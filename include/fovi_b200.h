@@ -215,6 +215,28 @@ int fovi_sample_knnconv_fused(const fovi_sampler_plan* sampler, fovi_knnconv_pla
                               int y_dtype, int relu, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Depthwise KNN convolution: out[b, c*g + j, n] = bias[c*g + j] + sum_k Xpad[b, c, idx[k,n]] * W[c, tap[n,k], j],
+ * g = c_out / c_in.  Replaces KNNDepthwiseConvLayer.forward (fovi/arch/knn.py:847-872) and the depthwise half of
+ * KNNDepthwiseSeparableConvLayer.forward (fovi/arch/knn.py:776-800).  `plan` is a fovi_knnconv_plan created with this
+ * layer's tables and channel counts (c_out a multiple of c_in).  Wp: DEVICE float32 [V, c_out], Wp[v][c*g + j] = W[c][v][j].
+ * X: [B,c_in,n_in] (FOVI_ACT_BCN) or [B,n_in,c_in] (FOVI_ACT_BNC); Y likewise with c_out, n_out.
+ * ------------------------------------------------------------------------------------------ */
+int fovi_knn_depthwise_forward(const fovi_knnconv_plan* plan, const void* X, int x_dtype, int x_layout, const float* Wp,
+                               const float* bias, void* Y, int y_dtype, int y_layout, int B, int relu, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Backward pass of KNNConv.  The reference gets its gradients from autograd through gather, one-hot matmul and linear
+ * (fovi/arch/knn.py:538-557).  Here both gradient contractions are run by fovi_knnconv_forward on derived plans (the
+ * transposed layer for the input gradient; for the weight gradient the batch takes the place of the channels, see
+ * fovi_b200/grad.py).  The one extra device routine is the layout change that puts the batch index innermost.
+ *
+ * src: logical [B, I, J] of `dtype`, element (b,i,j) at b*sb + i*si + j*sj (element strides; si == 1 or sj == 1).
+ * dst: [I, Jp, Bp] bf16, fully written: zeros where j >= J or b >= B.
+ * ------------------------------------------------------------------------------------------ */
+int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst, int Jp,
+                        int Bp, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Table construction on the host, with a reproducible rule for ties.
  * Replaces the neighbour search _compute_euclidean_distances_batched + topk (fovi/arch/knn.py:101-152) and
  * compute_local_rf (fovi/arch/knn.py:599-647).  The reference's float32 library calls rank the (frequent) exact and

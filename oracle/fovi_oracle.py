@@ -257,6 +257,25 @@ def knnconv_backward(X, knn_idx_pad, tap, V, weight, grad_out, dtype=np.float64)
     return (dXp[:, :, :Nin].astype(f32), dW.reshape(Cout, Cin * V).astype(f32), G.sum((0, 2)).astype(f32))
 
 
+def knn_depthwise_forward(X, knn_idx_pad, tap, weight, bias=None, dtype=np.float64):
+    """``KNNDepthwiseConvLayer.forward`` (fovi/arch/knn.py:847-872; also the depthwise half of the separable layer,
+    :776-800): ``out[b, c*g + j, n] = bias[c*g + j] + sum_k Xpad[b, c, idx[k,n]] * W[c, tap[n,k], j]``.
+    X [B,Cin,Nin]; weight [Cin, V, g]; returns [B, Cin*g, Nout] float32."""
+    X = np.asarray(X, dtype)
+    B, Cin, Nin = X.shape
+    K, Nout = knn_idx_pad.shape
+    W = np.asarray(weight, dtype)
+    g = W.shape[2]
+    Xp = np.concatenate([X, np.zeros((B, Cin, 1), dtype)], 2)
+    out = np.zeros((B, Cin, g, Nout), dtype)
+    for k in range(K):
+        out += Xp[:, :, None, knn_idx_pad[k]] * W[:, tap[:, k], :].transpose(0, 2, 1)[None]
+    out = out.reshape(B, Cin * g, Nout)
+    if bias is not None:
+        out = out + np.asarray(bias, dtype)[None, :, None]
+    return out.astype(f32)
+
+
 def knnconv_stack(X, layers, relu_between=True):
     """A chain of KNNConv layers with ReLU between them (the conv->ReLU skeleton of
     fovi/arch/knnalexnet.py:109-127 without norm/pool).  ``layers`` is a list of dicts

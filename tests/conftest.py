@@ -10,8 +10,20 @@ if ROOT not in sys.path:
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
+@pytest.fixture(autouse=True)
+def _inference_mode_by_default(request):
+    """Tests run with gradients disabled, as inference callers do; tests marked `autograd` keep them enabled."""
+    import torch
+    if request.node.get_closest_marker("autograd") is not None:
+        yield
+    else:
+        with torch.no_grad():
+            yield
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 with `-m gpu`)")
+    config.addinivalue_line("markers", "autograd: the test runs with gradients enabled")
 
 
 @pytest.fixture(scope="session")

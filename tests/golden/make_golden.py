@@ -164,10 +164,59 @@ def backward_fixture(save, knn):
     print("backward fixture: n_in", len(ic), "n_out", len(oc), "V", V)
 
 
+def depthwise_fixture(save, knn):
+    """Depthwise and depthwise-separable KNN convolution (fovi/arch/knn.py:722-872).  In the checkout this was generated
+    from, both layers' ``forward`` raise: ``_apply_local_rf`` returns ``[b, n, (d v)]`` and the next line rearranges it as a
+    4-D ``'b d v n'`` tensor.  The fixture therefore runs the reference layer's own gather (``_pad_and_gather_knns``) and
+    tap scatter (``_apply_local_rf``), views the result as ``[b, n, d, v]`` and applies the layers' own contraction
+    ``einsum('bndv,dvg->bndg')``, bias and pointwise ``nn.Linear``: the reference's steps with the one shape fixed."""
+    from einops import rearrange
+    ic, oc, _ = knn.get_in_out_coords(24, 16, 1.0, 2, style="isotropic", auto_match_cart_resources=0, device="cpu")
+    rs = np.random.RandomState(41)
+    x = rs.standard_normal((4, 16, len(ic))).astype(f32)
+    out = {"seed": np.int64(41)}
+    torch.manual_seed(6)
+    dw = knn.KNNDepthwiseConvLayer(16, 32, 9, ic, oc, device="cpu", ref_frame_side_length=4, bias=True)
+    try:
+        dw(torch.from_numpy(x))
+        raise AssertionError("the reference's depthwise forward runs now: record its output directly")
+    except AssertionError:
+        raise
+    except Exception as e:                                  # noqa: BLE001  (einops.EinopsError at this checkout)
+        print("reference KNNDepthwiseConvLayer.forward raises:", type(e).__name__)
+    V = dw.ref_coords.shape[0]
+    w = (rs.standard_normal((16, V, 2)) * 0.2).astype(f32)
+    b = (0.1 * rs.standard_normal(32)).astype(f32)
+
+    def steps(layer, weight):
+        f = layer._apply_local_rf(layer._pad_and_gather_knns(torch.from_numpy(x)))         # [b, n, (d v)]
+        f = rearrange(f, "b n (d v) -> b n d v", d=16)
+        return torch.einsum("bndv,dvg->bndg", f, torch.from_numpy(weight)).reshape(x.shape[0], f.shape[1], -1)
+
+    y = (steps(dw, w).transpose(1, 2) + torch.from_numpy(b)[None, :, None]).numpy()
+    t = layer_tables(dw)
+    o = oracle.knn_depthwise_forward(x, t["knn_idx_pad"], t["tap"].astype(np.int64), w, b)
+    assert rel_err(o, y) < 1e-5, rel_err(o, y)
+    out.update(t)
+    out["dw_out"] = y
+    sep = knn.KNNDepthwiseSeparableConvLayer(16, 32, 9, ic, oc, device="cpu", ref_frame_side_length=4, bias=True)
+    pw = (rs.standard_normal((32, 32)) * 0.2).astype(f32)
+    pb = (0.1 * rs.standard_normal(32)).astype(f32)
+    sep.p_conv.weight.data.copy_(torch.from_numpy(pw))
+    sep.p_conv.bias.data.copy_(torch.from_numpy(pb))
+    ys = sep.p_conv(steps(sep, w)).transpose(1, 2).numpy()
+    o2 = oracle.knn_depthwise_forward(x, t["knn_idx_pad"], t["tap"].astype(np.int64), w)
+    o2 = np.einsum("bcn,oc->bon", o2, pw) + pb[None, :, None]
+    assert rel_err(o2, ys) < 1e-5, rel_err(o2, ys)
+    out["dwsep_out"] = ys
+    save("depthwise_small.npz", **out)
+    print("depthwise fixture: n_in", len(ic), "n_out", len(oc), "V", V, "state keys", sorted(sep.state_dict().keys()), sorted(dw.state_dict().keys()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
-    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward"], help="regenerate one fixture group only")
+    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise"], help="regenerate one fixture group only")
     args = ap.parse_args()
     knn, retina, coords, knnvit = load_reference(args.reference)
     torch.set_grad_enabled(False)
@@ -176,6 +225,8 @@ def main():
         return alexnet_fixture(save)
     if args.only == "backward":
         return backward_fixture(save, knn)
+    if args.only == "depthwise":
+        return depthwise_fixture(save, knn)
 
     # ------------------------------------------------------------ sensors (geometry fixtures)
     sensors = {}
@@ -343,6 +394,7 @@ def main():
 
     alexnet_fixture(save)
     backward_fixture(save, knn)
+    depthwise_fixture(save, knn)
 
 
 if __name__ == "__main__":

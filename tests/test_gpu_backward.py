@@ -7,7 +7,7 @@ import torch
 from conftest import kaiming_weight
 from oracle import fovi_oracle as oracle
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.autograd]
 TOL = 1e-2          # relative L2, bf16 operands with float32 accumulation vs float32 reference
 
 

@@ -147,3 +147,14 @@ def test_oracle_backward_matches_reference_autograd(golden):
     dX, dW, db = oracle.knnconv_backward(x, g["knn_idx_pad"], g["tap"].astype(np.int64), V, w, gy)
     for a, r in ((dX, g["dX"]), (dW, g["dW"]), (db, g["dbias"])):
         assert np.abs(a - r).max() <= 1e-5 * np.abs(r).max()
+
+
+def test_oracle_depthwise_matches_reference_steps(golden):
+    g = golden("depthwise_small.npz")
+    V = int(g["V"])
+    rs = np.random.RandomState(int(g["seed"]))
+    x = rs.standard_normal((4, 16, int(g["n_in"]))).astype(np.float32)
+    w = (rs.standard_normal((16, V, 2)) * 0.2).astype(np.float32)
+    b = (0.1 * rs.standard_normal(32)).astype(np.float32)
+    o = oracle.knn_depthwise_forward(x, g["knn_idx_pad"], g["tap"].astype(np.int64), w, b)
+    assert np.abs(o - g["dw_out"]).max() <= 1e-5 * np.abs(g["dw_out"]).max()
