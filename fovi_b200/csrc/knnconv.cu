@@ -43,6 +43,36 @@ __global__ void pack_weights_pairs_kernel(const TW* __restrict__ W, __nv_bfloat1
   }
 }
 
+// Packed weights of a GROUPED pair-mode plan: the plan's "output points" are groups of G consecutive output points of the
+// layer and its "output channels" are the G members' channels side by side (c_out = G * co), so the group's one
+// neighbour list is the union of its members' lists.  The plan was created with tap[g][k] = k, i.e. pair_tap holds each
+// slot's position in the union list; member_tap[g][k][j] is the filter tap member j gives that neighbour (0xFFFF: it
+// is not a neighbour of member j, the weight is zero).  Same destination layout as pack_weights_pairs_kernel.
+template <typename TW>
+__global__ void pack_weights_grouped_kernel(const TW* __restrict__ W, __nv_bfloat16* __restrict__ dst,
+                                            const uint16_t* __restrict__ pair_tap, const uint16_t* __restrict__ member_tap, int n_groups,
+                                            int sp, int K, int G, int V, int co, int c_in, int ct) {
+  const int c_out = G * co;
+  const long long total = (long long)n_groups * sp * c_out * 8;
+  const int n_ct = c_out / ct;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int e = (int)(i & 7);
+    long long r = i >> 3;
+    const int oc = (int)(r % ct); r /= ct;
+    const int sl = (int)(r % sp); r /= sp;
+    const int tile = (int)(r % n_ct);
+    const long long g = r / n_ct;
+    const int op = tile * ct + oc;          // channel of the group: member j, its channel o
+    const int j = op / co, o = op - j * co;
+    const int h = e >> 2, c = e & 3;
+    const int k = pair_tap[(g * sp + sl) * 2 + h];
+    int t = 0xFFFF;
+    if (k != 0xFFFF) t = member_tap[(g * K + k) * G + j];
+    const float w = (c < c_in && t != 0xFFFF) ? ld_as_float(W + ((long long)o * c_in + c) * V + t) : 0.f;
+    dst[i] = __float2bfloat16_rn(w);
+  }
+}
+
 // X [B,C,N] -> [ceil(B/128), ceil(N/2), 128, 2, 4] bf16 (pair layout), one thread per (pair, image).
 template <typename TX>
 __global__ void pack_points_pairs_kernel(const TX* __restrict__ x, __nv_bfloat16* __restrict__ dst, int B, int C, int N) {
@@ -279,6 +309,22 @@ extern "C" int fovi_knnconv_pack_weights(const fovi_knnconv_plan* p, const void*
   else PACK(__nv_bfloat16, __nv_bfloat16);
 #undef PACK
   return fovi::after_launch("pack_weights_kernel");
+}
+
+extern "C" int fovi_knnconv_pack_weights_grouped(const fovi_knnconv_plan* p, const void* W, int w_dtype, const uint16_t* member_tap, int G,
+                                                 int V, void* dst, void* stream) {
+  if (!p || !W || !member_tap || !dst || !fovi::valid_dtype(w_dtype) || G <= 0 || V <= 0) return FOVI_ERR_INVALID_ARGUMENT;
+  if (p->x_layout != FOVI_X_PAIRS || !p->ct || p->c_out % G) return FOVI_ERR_UNSUPPORTED;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long tot = (long long)p->n_out * p->sp * p->c_out * 8;
+  const int grid = (int)std::min<long long>((tot + 255) / 256, 148 * 32);
+  if (w_dtype == FOVI_F32)
+    pack_weights_grouped_kernel<float><<<grid, 256, 0, st>>>((const float*)W, (__nv_bfloat16*)dst, p->pair_tap, member_tap, p->n_out, p->sp, p->K,
+                                                             G, V, p->c_out / G, p->c_in, p->ct);
+  else
+    pack_weights_grouped_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)W, (__nv_bfloat16*)dst, p->pair_tap, member_tap, p->n_out,
+                                                                     p->sp, p->K, G, V, p->c_out / G, p->c_in, p->ct);
+  return fovi::after_launch("pack_weights_grouped_kernel");
 }
 
 extern "C" int fovi_pack_points(const void* x, int x_dtype, int B, int C, int N, void* dst, int cp, int x_layout, void* stream) {

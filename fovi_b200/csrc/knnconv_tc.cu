@@ -127,34 +127,52 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const uint16_t* tb_tap = reinterpret_cast<const uint16_t*>(tbl0 + buf * tbl_pitch + (size_t)a.kp * 4);
       const int m0 = mt * BM, o0 = ctile * a.ct;
       if (MODE == MODE_PAIRS) {
-        // The whole warp issues: lane j < 8 copies the 2 KB block of slot j, lane 8 the eight weight slabs.
-        // (A single thread pays the full issue cost of every copy in sequence; nine lanes pay it once.)
+        // The whole warp issues, several stages per pass: the warp is cut into groups of nine lanes, group j takes stage
+        // st0 + j; its first lane waits for that stage to be free and arms its barrier, then lane i < 8 copies the 2 KB
+        // blocks starting at slot i and lane 8 the eight weight slabs.  (A single thread pays the wait and the full issue
+        // cost of every copy in sequence, about a thousand cycles per stage; here a pass costs that once for a.pgroups
+        // stages.  pgroups < nstage, so the consumer always has a loaded stage while the producer waits;
+        // two stages per pass measured best: 154 / 126 / 148 us with 1 / 2 / 3 on the grouped 3->64 first layer.)
         const int steps = (cnt + 7) / 8;
         const uint32_t b_bytes = 8u * (uint32_t)a.ct * 16u;
         const unsigned char* wn = a.Wt + ((size_t)n * a.n_ct + ctile) * a.kp * ((size_t)a.ct * 16);
         const unsigned char* xt = a.X + (size_t)mt * a.n_pairs * 2048;  // this batch tile's pair blocks
-        for (int st = 0; st < steps; ++st) {
-          const uint32_t full = smem_u32(&hdr->full[s]);
-          if (lane == 0) {
-            ok = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit);
-            if (ok) mbar_expect_tx(full, a.stage_bytes);
+        const int grp = lane / 9, gl = lane - grp * 9;
+        for (int st0 = 0; st0 < steps; st0 += a.pgroups) {
+          const int my_st = st0 + grp;
+          const bool active = grp < a.pgroups && my_st < steps;
+          uint32_t my_s = s + (uint32_t)grp, my_ph = ph;
+          if (my_s >= (uint32_t)a.nstage) { my_s -= (uint32_t)a.nstage; my_ph ^= 1u; }
+          const uint32_t full = smem_u32(&hdr->full[my_s]);
+          bool mine = true;
+          if (active && gl == 0) {
+            mine = mbar_wait(smem_u32(&hdr->empty[my_s]), my_ph ^ 1u, abort_flag, a.status, 1, a.wait_limit);
+            if (mine) mbar_expect_tx(full, a.stage_bytes);
           }
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          ok = __all_sync(0xffffffffu, mine);   // also: nobody copies into a stage before its group's first lane saw it free
           if (!ok) break;
-          const uint32_t sa = stages0 + s * a.stage_bytes;
-          if (lane < 8) {
-            // the plan marked the first slot of every run of consecutive pairs with the run's length (the unused
-            // tail, whose slots hold n_pairs, is one run of zeros): one copy per run
-            const uint32_t len = tb_tap[st * 8 + lane];
-            if (len) {
-              const int pr = tb_idx[st * 8 + lane];
-              bulk_load(sa + lane * 2048u, pr < a.n_pairs ? xt + (size_t)pr * 2048 : a.zero_block, len * 2048u, full);
+          // one copy per lane, all issued by the same instruction
+          uint32_t dst = 0, bytes = 0;
+          const unsigned char* src = nullptr;
+          if (active) {
+            const uint32_t sa = stages0 + my_s * a.stage_bytes;
+            if (gl < 8) {
+              // the plan marked the first slot of every run of consecutive pairs with the run's length (the unused
+              // tail, whose slots hold n_pairs, is one run of zeros): one copy per run
+              const uint32_t len = tb_tap[my_st * 8 + gl];
+              if (len) {
+                const int pr = tb_idx[my_st * 8 + gl];
+                dst = sa + gl * 2048u; src = pr < a.n_pairs ? xt + (size_t)pr * 2048 : a.zero_block; bytes = len * 2048u;
+              }
+            } else {
+              dst = sa + b_stage_off; src = wn + (size_t)my_st * b_bytes; bytes = b_bytes;
             }
-          } else if (lane == 8) {
-            bulk_load(sa + b_stage_off, wn + (size_t)st * b_bytes, b_bytes, full);
           }
-          ++issued;
-          if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+          if (bytes) bulk_load(dst, src, bytes, full);
+          const uint32_t done = (uint32_t)min(a.pgroups, steps - st0);
+          issued += done;
+          s += done;
+          if (s >= (uint32_t)a.nstage) { s -= (uint32_t)a.nstage; ph ^= 1u; }
         }
       } else if (lane == 0) {
         if (C64) {
@@ -225,10 +243,10 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.ct >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t s = 0, ph = 0, acc = 0, aph = 0;
       bool ok = true;
-      int cnt = blockIdx.x < a.total_items ? __ldg(a.nbr_cnt + (blockIdx.x / a.n_ct) % a.n_out) : 0;
+      int cnt = blockIdx.x < a.total_items ? __ldg(a.nbr_cnt + item_point(a, blockIdx.x)) : 0;
       for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
         const int next = item + gridDim.x;
-        const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;  // consumed next round
+        const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + item_point(a, next)) : 0;  // consumed next round
         const int steps = C64 ? cnt * chunks : (cnt * chunks + 7) / 8;
         if (!mbar_wait(smem_u32(&hdr->acc_empty[acc]), aph ^ 1u, abort_flag, a.status, 2, a.wait_limit)) { ok = false; break; }
         tc_fence_after();
@@ -268,12 +286,12 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const int q = warp & 3;  // tensor-memory lane quarter this warp may read
     uint32_t acc = 0, aph = 0;
     bool ok = true;
-    int cnt = blockIdx.x < a.total_items ? __ldg(a.nbr_cnt + (blockIdx.x / a.n_ct) % a.n_out) : 0;
+    int cnt = blockIdx.x < a.total_items ? __ldg(a.nbr_cnt + item_point(a, blockIdx.x)) : 0;
     for (int item = blockIdx.x; item < a.total_items && ok; item += gridDim.x) {
       int n, mt, ctile;
       decode_item(a, item, n, mt, ctile);
       const int next = item + gridDim.x;
-      const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + (next / a.n_ct) % a.n_out) : 0;
+      const int cnt_next = next < a.total_items ? __ldg(a.nbr_cnt + item_point(a, next)) : 0;
       ok = mbar_wait(smem_u32(&hdr->acc_full[acc]), aph, abort_flag, a.status, 4, a.wait_limit);
       ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-collective: leave as a whole warp or not at all
       if (!ok) break;
@@ -399,6 +417,7 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
   a.wait_limit = wait_limit; a.skip_loads = skip_loads;
+  a.mt_fastest = (pairs && !getenv("FOVI_B200_POINT_FASTEST")) ? 1 : 0;
   const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
   if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;
@@ -416,6 +435,8 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   const uint32_t budget = (ctas_per_sm == 3 ? 73u : ctas_per_sm == 2 ? 110u : 220u) * 1024u - 2048u - a.table_bytes;
   a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
   if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;
+  static const int pair_groups = getenv("FOVI_B200_PAIR_GROUPS") ? atoi(getenv("FOVI_B200_PAIR_GROUPS")) : 2;
+  a.pgroups = std::max(1, std::min(std::min(pair_groups, 3), a.nstage - 1));
   const size_t smem = 1024 /*align slack*/ + 1024 /*header*/ + a.table_bytes + (size_t)a.nstage * a.stage_bytes;
 
   CUtensorMap tmA, tmB;

@@ -25,6 +25,8 @@ struct TcArgs {
   int ct, n_ct, n_mt, nstage, relu, y_f32, total_items;
   uint32_t wait_limit;   // try_wait attempts before a wait gives up
   int skip_loads;        // self-test: the producer withholds every operand load, so the first consumer wait must give up
+  int mt_fastest;        // item order, see decode_item
+  int pgroups;           // pair mode: stages the producer warp fills per pass
   uint32_t acc_cols, tmem_cols;  // columns per accumulator (power of two >= ct) and allocated in total (two accumulators)
   const unsigned char* X; const unsigned char* Wt; const unsigned char* zero_block; int n_pairs;  // PAIRS mode
   uint32_t stage_bytes, table_bytes;
@@ -128,11 +130,18 @@ struct SmemHeader {
 
 constexpr int TBQ = 8;  // table entries prefetched per producer lane: list pitch <= 32 * TBQ
 
+// Work item -> (output point, batch tile, c_out tile).  Consecutive items run at the same time on neighbouring SMs:
+// with the point varying fastest they share activations (neighbouring points read the same inputs), with the batch
+// tile varying fastest (mt_fastest, pair mode) they share the point's packed weights, which are the larger operand there.
 __device__ __forceinline__ void decode_item(const TcArgs& a, int item, int& n, int& mt, int& ctile) {
   ctile = item % a.n_ct;
   const int t = item / a.n_ct;
-  n = t % a.n_out;
-  mt = t / a.n_out;
+  if (a.mt_fastest) { mt = t % a.n_mt; n = t / a.n_mt; }
+  else { n = t % a.n_out; mt = t / a.n_out; }
+}
+__device__ __forceinline__ int item_point(const TcArgs& a, int item) {
+  const int t = item / a.n_ct;
+  return a.mt_fastest ? t / a.n_mt : t % a.n_out;
 }
 
 

@@ -1,6 +1,7 @@
 """Tensor-level wrappers over the C ABI: plans own device tables, functions take torch CUDA
 tensors, pass raw pointers and the current stream, and allocate outputs with torch."""
 import ctypes as C
+import os
 
 import numpy as np
 import torch
@@ -91,7 +92,10 @@ def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=No
 class KnnConvPlan:
     """Device copy of one layer's compacted neighbour/tap tables (fovi_knnconv_plan)."""
 
-    def __init__(self, knn_idx_pad, tap, n_in, V, c_in, c_out, device=None):
+    def __init__(self, knn_idx_pad, tap, n_in, V, c_in, c_out, device=None, group=None):
+        """`group`: output points per accumulator of a pair-layout (c_in <= 4) layer's tensor-core path; None picks the
+        largest of 4, 3, 2 that divides n_out and keeps group*c_out <= 256 (1 = no grouping; the environment variable
+        FOVI_B200_NO_GROUPING forces 1)."""
         idx = np.ascontiguousarray(np.asarray(knn_idx_pad, np.int32))
         tp = np.ascontiguousarray(np.asarray(tap, np.uint16))
         K, n_out = idx.shape
@@ -108,11 +112,74 @@ class KnnConvPlan:
         self.x_layout = lib.fovi_knnconv_x_layout(h)
         self.tc_supported = bool(lib.fovi_knnconv_tc_supported(h))
         self.n_pairs = (self.n_in + 1) // 2
+        self.group, self._hg, self._member_tap, self._bias_g = 1, None, None, None
+        if self.x_layout == X_PAIRS and self.tc_supported and group != 1 and not os.environ.get("FOVI_B200_NO_GROUPING"):
+            self._make_grouped(idx, tp, (int(group),) if group else (4, 3, 2))
+
+    def _make_grouped(self, idx, tp, candidates):
+        """A second plan whose "points" are groups of G consecutive output points (G*c_out channels side by side) and whose
+        neighbour lists are the unions of the members' lists: with 3-4 input channels an MMA over one point's 64-96 output
+        channels costs as much to issue as one over 256, and consecutive points share most of their neighbours."""
+        n_in, n_out, K = self.n_in, self.n_out, self.K
+        for G in candidates:
+            if G < 2 or n_out % G or G * self.c_out > 256:
+                continue
+            ng = n_out // G
+            cols = idx.T.reshape(ng, G * K).astype(np.int64)               # members' lists side by side
+            taps = tp.reshape(ng, G * K).astype(np.int64)
+            member = np.repeat(np.arange(G), K)[None, :].repeat(ng, 0)
+            order = np.argsort(cols, axis=1, kind="stable")
+            sc = np.take_along_axis(cols, order, 1)
+            first = np.ones_like(sc, dtype=bool)
+            first[:, 1:] = sc[:, 1:] != sc[:, :-1]
+            first &= sc != n_in                                              # pad entries join no list
+            pos = np.cumsum(first, 1) - 1                                    # position of each entry's point in the union list
+            mem = np.take_along_axis(member, order, 1)
+            dup = (sc[:, 1:] == sc[:, :-1]) & (mem[:, 1:] == mem[:, :-1]) & (sc[:, 1:] != n_in)
+            if dup.any():                                                    # a member lists a point twice: leave the layer ungrouped
+                return
+            ku = int(first.sum(1).max())
+            if ku > 256 or ku >= 0xFFFF:
+                continue
+            kq = -(-ku // 8) * 8
+            uidx = np.full((kq, ng), n_in, np.int32)
+            mtap = np.full((ng, kq, G), 0xFFFF, np.uint16)
+            rows = np.arange(ng)[:, None].repeat(G * K, 1)
+            valid = sc != n_in
+            uidx[pos[valid], rows[valid]] = sc[valid]
+            mtap[rows[valid], pos[valid], mem[valid]] = np.take_along_axis(taps, order, 1)[valid]
+            utap = np.ascontiguousarray(np.arange(kq, dtype=np.uint16)[None, :].repeat(ng, 0))   # tap = position in the union list
+            hg = C.c_void_p()
+            uidx = np.ascontiguousarray(uidx)
+            with torch.cuda.device(self.device):
+                check(lib.fovi_knnconv_plan_create(uidx.ctypes.data_as(C.c_void_p), utap.ctypes.data_as(C.c_void_p), n_in, ng, kq, kq,
+                                                   self.c_in, G * self.c_out, C.byref(hg)), "fovi_knnconv_plan_create")
+            if not lib.fovi_knnconv_tc_supported(hg):
+                lib.fovi_knnconv_plan_destroy(hg)
+                continue
+            self.group, self._hg, self._kq = G, hg, kq
+            self._member_tap = torch.from_numpy(mtap.view(np.int16)).to(self.device)
+            return
+
+    @property
+    def _h_tc(self):
+        """Handle the tensor-core entry points take: the grouped plan when there is one."""
+        return self._hg if self._hg else self._h
+
+    def _tc_bias(self, bias):
+        if bias is None or self.group == 1:
+            return bias
+        key = (bias.data_ptr(), bias._version)
+        if self._bias_g is None or self._bias_g[0] != key:
+            self._bias_g = (key, bias.detach().float().repeat(self.group).contiguous())
+        return self._bias_g[1]
 
     def __del__(self):
-        h, self._h = getattr(self, "_h", None), None
-        if h and lib is not None:
-            lib.fovi_knnconv_plan_destroy(h)
+        for name in ("_h", "_hg"):
+            h = getattr(self, name, None)
+            setattr(self, name, None)
+            if h and lib is not None:
+                lib.fovi_knnconv_plan_destroy(h)
 
     def flops_per_image(self):
         """Algorithmic FLOPs of one forward for one image: 2 * c_in * c_out * nnz."""
@@ -124,6 +191,14 @@ class KnnConvPlan:
         _need_cuda(weight)
         weight = weight.detach().contiguous()
         assert weight.shape == (self.c_out, self.c_in * self.V)
+        if self._hg and dtype == torch.bfloat16:
+            nbytes = lib.fovi_knnconv_packed_weight_bytes(self._hg, _dt(dtype))
+            ng, cg = self.n_out // self.group, self.group * self.c_out
+            dst = torch.empty((ng, nbytes // (ng * cg * 16), cg, 8), dtype=dtype, device=weight.device)
+            with torch.cuda.device(weight.device):
+                check(lib.fovi_knnconv_pack_weights_grouped(self._hg, _ptr(weight), _dt(weight.dtype), _ptr(self._member_tap), self.group, self.V,
+                                                            _ptr(dst), _stream()), "fovi_knnconv_pack_weights_grouped")
+            return dst
         nbytes = lib.fovi_knnconv_packed_weight_bytes(self._h, _dt(dtype))
         if self.x_layout == X_PAIRS and dtype == torch.bfloat16:
             dst = torch.empty((self.n_out, nbytes // (self.n_out * self.c_out * 16), self.c_out, 8), dtype=dtype, device=weight.device)  # memory order [n_out, c_out tiles, slots, tile, 8]
@@ -142,17 +217,17 @@ class KnnConvPlan:
         if self.x_layout == X_PAIRS:
             B = x_bnc.shape[0] * 128 if batch is None else int(batch)
             assert x_bnc.shape == ((B + 127) // 128, self.n_pairs, 128, 8), (x_bnc.shape, B)
-            assert wt.dim() == 4 and wt.shape[0] == self.n_out and wt.shape[2:] == (self.c_out, 8), wt.shape
+            assert wt.dim() == 4 and wt.shape[0] == self.n_out // self.group and wt.shape[2:] == (self.group * self.c_out, 8), wt.shape
         else:
             B = x_bnc.shape[0]
             assert x_bnc.shape[1:] == (self.n_in, self.cin_packed), x_bnc.shape
             assert wt.shape == (self.V, self.c_out, self.cin_packed)
         if bias is not None:
-            bias = bias.detach().to(torch.float32).contiguous()
+            bias = self._tc_bias(bias).detach().to(torch.float32).contiguous()
         if out is None:
             out = torch.empty((B, self.n_out, self.c_out), dtype=out_dtype, device=x_bnc.device)
-        with torch.cuda.device(x_bnc.device):
-            check(lib.fovi_knnconv_forward(self._h, _ptr(x_bnc), _ptr(wt), _ptr(bias) if bias is not None else None, _ptr(out),
+        with torch.cuda.device(x_bnc.device):   # a grouped plan writes [B, n_out/G, G*c_out]: the same memory
+            check(lib.fovi_knnconv_forward(self._h_tc, _ptr(x_bnc), _ptr(wt), _ptr(bias) if bias is not None else None, _ptr(out),
                                            _dt(out.dtype), B, int(relu), _stream()), "fovi_knnconv_forward")
         return out
 
@@ -179,7 +254,7 @@ class KnnConvPlan:
         B = (x_bnc.shape[0] * 128 if batch is None else int(batch)) if self.x_layout == X_PAIRS else x_bnc.shape[0]
         out = torch.zeros((B, self.n_out, self.c_out), dtype=out_dtype, device=x_bnc.device)
         with torch.cuda.device(x_bnc.device):
-            check(lib.fovi_knnconv_selftest_wait_timeout(self._h, _ptr(x_bnc), _ptr(wt), _ptr(out), _dt(out.dtype), B, _stream()),
+            check(lib.fovi_knnconv_selftest_wait_timeout(self._h_tc, _ptr(x_bnc), _ptr(wt), _ptr(out), _dt(out.dtype), B, _stream()),
                   "fovi_knnconv_selftest_wait_timeout")
 
     def depthwise(self, x, wp, bias=None, relu=False, x_layout=ACT_BCN, y_layout=ACT_BCN, out_dtype=None):
@@ -204,6 +279,8 @@ class KnnConvPlan:
         """Synchronise the current stream and raise if a tensor-core launch gave up on a wait."""
         with torch.cuda.device(self.device):
             check(lib.fovi_knnconv_check(self._h, _stream()), "fovi_knnconv_check")
+            if self._hg:
+                check(lib.fovi_knnconv_check(self._hg, _stream()), "fovi_knnconv_check")
 
 
 def sample_knnconv_fused(splan, cplan, img, fix_rc, fix_hw, wt, bias=None, relu=False, mode=BILINEAR, pad=PAD_ZEROS,
@@ -212,17 +289,17 @@ def sample_knnconv_fused(splan, cplan, img, fix_rc, fix_hw, wt, bias=None, relu=
     _need_cuda(img, fix_rc, fix_hw, wt, bias)
     B, Cc, H, W = img.shape
     F = fix_rc.shape[1]
-    need = lib.fovi_fused_intermediate_bytes(cplan._h, B * F)
+    need = lib.fovi_fused_intermediate_bytes(cplan._h_tc, B * F)
     if intermediate is None:
         intermediate = torch.zeros(need // 2, dtype=torch.bfloat16, device=img.device)
     assert intermediate.numel() * intermediate.element_size() >= need
     if out is None:
         out = torch.empty((B * F, cplan.n_out, cplan.c_out), dtype=out_dtype, device=img.device)
     if bias is not None:
-        bias = bias.detach().to(torch.float32).contiguous()
+        bias = cplan._tc_bias(bias).detach().to(torch.float32).contiguous()
     strides = (C.c_int64 * 4)(*img.stride())
     with torch.cuda.device(img.device):
-        check(lib.fovi_sample_knnconv_fused(splan._h, cplan._h, _ptr(img), _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc.contiguous()),
+        check(lib.fovi_sample_knnconv_fused(splan._h, cplan._h_tc, _ptr(img), _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc.contiguous()),
                                             _ptr(fix_hw.contiguous()), F, mode, pad, _ptr(intermediate), _ptr(wt),
                                             _ptr(bias) if bias is not None else None, _ptr(out), _dt(out.dtype), int(relu), _stream()),
               "fovi_sample_knnconv_fused")

@@ -148,6 +148,16 @@ int fovi_knnconv_pack_weights(const fovi_knnconv_plan* plan, const void* W, int 
 /* Bytes of the packed weight buffer for `dst_dtype`. */
 int64_t fovi_knnconv_packed_weight_bytes(const fovi_knnconv_plan* plan, int dst_dtype);
 
+/* Grouped first layer.  With c_in <= 4 the MMA's N axis holds only c_out (64-96) columns; G consecutive output points can
+ * share one accumulator instead: create the plan for n_out/G "points" with G*c_out "channels", the neighbour list of
+ * group g being the union of its members' lists (knn_idx_pad[k][g]) and tap[g][k] = k.  This call packs the weights for
+ * such a plan: W is the layer's [c_out, c_in*V] weight, member_tap DEVICE uint16 [n_out/G, K, G] gives for union entry k
+ * of group g the tap member j uses for it (0xFFFF: none).  The forward call is unchanged and its output
+ * [B, n_out/G, G*c_out] is the layer's [B, n_out, c_out] as it stands.  No counterpart in the reference (its forward,
+ * fovi/arch/knn.py:538-557, has no such tiling concern). */
+int fovi_knnconv_pack_weights_grouped(const fovi_knnconv_plan* plan, const void* W, int w_dtype, const uint16_t* member_tap, int G,
+                                      int V, void* dst, void* stream);
+
 /* Convert activations [B,C,N] (x_dtype, contiguous) to a tensor-core input layout:
  * x_layout FOVI_X_BNC: [B,N,cp] bf16 with zero-filled pad channels (cp >= C, multiple of 8);
  * x_layout FOVI_X_PAIRS: [ceil(B/128),ceil(N/2),128,2,4] bf16 (C <= 4; cp ignored). */

@@ -54,7 +54,7 @@ def test_static_scratch_matches_regular_entry_points(golden):
     # pair layout (c_in = 3): ragged batch first, then a larger one that reuses and overwrites the array
     g = golden("config1.npz")
     V, n_in = int(g["V"]), int(g["n_in"])
-    plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], n_in, V, 3, 64)
+    plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], n_in, V, 3, 64, group=1)   # the C entry point under test takes the plain plan
     _check_two_calls(ops, lib, plan, kaiming_weight(np.random.RandomState(1), 64, 3, V), 3, n_in, (5, 130))
     # channels-last layout (c_in = 64)
     t = golden("config3_tables.npz")
