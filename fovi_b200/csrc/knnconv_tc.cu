@@ -144,14 +144,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           uint32_t my_s = s + (uint32_t)grp, my_ph = ph;
           if (my_s >= (uint32_t)a.nstage) { my_s -= (uint32_t)a.nstage; my_ph ^= 1u; }
           const uint32_t full = smem_u32(&hdr->full[my_s]);
-          bool mine = true;
-          if (active && gl == 0) {
-            mine = mbar_wait(smem_u32(&hdr->empty[my_s]), my_ph ^ 1u, abort_flag, a.status, 1, a.wait_limit);
-            if (mine) mbar_expect_tx(full, a.stage_bytes);
-          }
-          ok = __all_sync(0xffffffffu, mine);   // also: nobody copies into a stage before its group's first lane saw it free
-          if (!ok) break;
-          // one copy per lane, all issued by the same instruction
+          // what this lane will copy, worked out before the wait (one copy per lane, all issued by the same instruction)
           uint32_t dst = 0, bytes = 0;
           const unsigned char* src = nullptr;
           if (active) {
@@ -168,6 +161,13 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
               dst = sa + b_stage_off; src = wn + (size_t)my_st * b_bytes; bytes = b_bytes;
             }
           }
+          bool mine = true;
+          if (active && gl == 0) {
+            mine = mbar_wait(smem_u32(&hdr->empty[my_s]), my_ph ^ 1u, abort_flag, a.status, 1, a.wait_limit);
+            if (mine) mbar_expect_tx(full, a.stage_bytes);
+          }
+          ok = __all_sync(0xffffffffu, mine);   // also: nobody copies into a stage before its group's first lane saw it free
+          if (!ok) break;
           if (bytes) bulk_load(dst, src, bytes, full);
           const uint32_t done = (uint32_t)min(a.pgroups, steps - st0);
           issued += done;
