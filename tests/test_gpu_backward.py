@@ -51,9 +51,9 @@ def test_gradients_match_reference_autograd(golden):
     assert layer.weight.grad.shape == layer.weight.shape and xt.grad.shape == xt.shape
 
 
-def test_first_layer_weight_gradient_and_split_lists(golden):
-    """A 3-channel first layer (pair-layout forward): its input needs no gradient; with K=49 neighbours per output and 49
-    taps every tap's pair list is longer than the kernel's limit and is split."""
+def test_first_layer_weight_gradient(golden):
+    """A 3-channel first layer (pair-layout forward): its weight gradient runs as one GEMM per output point (columns =
+    neighbour x channel, contraction over the batch) followed by a scatter-add onto the taps; its input needs no gradient."""
     g = golden("config1.npz")
     V, n_in = int(g["V"]), int(g["n_in"])
     n_out = g["knn_idx_pad"].shape[1]
@@ -74,7 +74,8 @@ def test_first_layer_weight_gradient_and_split_lists(golden):
     y8 = layer(torch.from_numpy(x[:8]).cuda())
     y8.backward(torch.from_numpy(gy[:8]).cuda())
     assert rel_l2(layer.weight.grad.cpu().numpy(), dW) < TOL
-    assert layer.grad_plans.dw_plan(64)[0].n_out > V                # lists were split
+    assert layer.grad_plans._few is not None                        # the per-point path ran
+    assert layer.grad_plans.dw_plan(64)[0].n_out > V                # the per-tap path would cut its 3800-entry lists
     with pytest.raises(NotImplementedError):
         xt = torch.from_numpy(x[:8]).cuda().requires_grad_(True)
         layer(xt).sum().backward()
