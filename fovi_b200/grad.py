@@ -22,7 +22,7 @@ import torch
 
 from . import ops
 
-__all__ = ["KnnConvGrad", "knnconv_autograd"]
+__all__ = ["KnnConvGrad", "knnconv_autograd", "knnconv_points_autograd"]
 
 MAX_LIST = 256      # longest neighbour list the tensor-core kernel takes
 
@@ -181,8 +181,49 @@ class _KnnConvFunction(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             gw = g.weight_grad(gy, x).to(weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = gy.float().sum((0, 2))
+            gb = gy.sum((0, 2), dtype=torch.float32)
         return gx, gw, gb, None
+
+
+class _KnnConvPointsFunction(torch.autograd.Function):
+    """A layer on the kernels' own activation layout (channels last, bf16) with the ReLU fused, so that a chain of layers
+    trains without a layout change between them.  `x` is [B, n_in, c_in] bf16, or for a pair-layout first layer the
+    [B, c_in, n_in] input itself (it is packed here)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, layer, relu):
+        plan = layer.plan
+        first = plan.x_layout == ops.X_PAIRS
+        rows = x.shape[0]
+        with torch.no_grad():
+            xp = ops.pack_points(x, plan) if first else x.contiguous()
+            y = plan.forward(xp, layer.packed_weight(), bias, relu=relu, out_dtype=torch.bfloat16, batch=rows)
+        ctx.layer, ctx.relu, ctx.first, ctx.has_bias = layer, relu, first, bias is not None
+        ctx.save_for_backward(x, weight, y if relu else None)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight, y = ctx.saved_tensors
+        g = ctx.layer.grad_plans
+        gy = gy.to(torch.bfloat16)
+        if ctx.relu:
+            gy = torch.ops.aten.threshold_backward(gy, y, 0)       # gy where y > 0, else 0: one pass
+        gy = gy.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            if ctx.first:
+                raise NotImplementedError("input gradient of a pair-layout first layer is not built")
+            gx = g.input_grad(gy, weight)                                      # [B, n_in, c_in] bf16
+        if ctx.needs_input_grad[1]:
+            gw = g.weight_grad(gy.permute(0, 2, 1), x if ctx.first else x.permute(0, 2, 1)).to(weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = gy.sum((0, 1), dtype=torch.float32)
+        return gx, gw, gb, None, None
+
+
+def knnconv_points_autograd(layer, x, relu):
+    return _KnnConvPointsFunction.apply(x, layer.weight, layer.bias, layer, relu)
 
 
 def knnconv_autograd(layer, x):

@@ -338,9 +338,28 @@ class KNNConvStack(nn.Module):
             h = L.forward_points(h, batch=rows, relu=(not last) or self.final_relu, out=bufs[i])
         return h
 
-    @torch.no_grad()
     def forward(self, X):
-        """X [B,C_in,N_in] -> [B,C_out,N_out] (channels-last view), dtype of X."""
+        """X [B,C_in,N_in] -> [B,C_out,N_out] (channels-last view), dtype of X.  With gradients enabled the chain is
+        differentiable and stays in the kernels' layout in both directions (fovi_b200/grad.py)."""
+        if torch.is_grad_enabled() and any(p.requires_grad for p in self.parameters()):
+            return self._forward_autograd(X)
+        with torch.no_grad():
+            return self._forward_inference(X)
+
+    def _forward_autograd(self, X):
+        from .grad import knnconv_points_autograd
+        if not all(L.plan.tc_supported and L.precision == "bf16" for L in self.layers):
+            raise RuntimeError("the backward pass is built for the bf16 tensor-core path")
+        first = self.layers[0].plan.x_layout == ops.X_PAIRS
+        if not first and self.layers[0].in_channels % 8:
+            raise RuntimeError("the first layer's channels must be at most 4 or a multiple of 8")
+        h = X if first else X.permute(0, 2, 1).to(torch.bfloat16)     # differentiable layout change
+        n = len(self.layers)
+        for i, L in enumerate(self.layers):
+            h = knnconv_points_autograd(L, h, (i < n - 1) or self.final_relu)
+        return h.permute(0, 2, 1).to(X.dtype)
+
+    def _forward_inference(self, X):
         xp = ops.pack_points(X, self.layers[0].plan)
         out_dtype = torch.float32 if X.dtype == torch.float32 else torch.bfloat16
         return self.forward_points(xp, X.shape[0], out_dtype).permute(0, 2, 1)

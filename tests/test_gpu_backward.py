@@ -109,3 +109,38 @@ def y_is_fresh(layer, x):
         layer.refresh_weights()
         b = layer(x)
     return torch.equal(a, b)
+
+
+def test_stack_trains_in_the_kernel_layout():
+    """KNNConvStack under autograd (channels-last between layers, ReLU fused) against the same layers called one by one
+    with torch's ReLU between them."""
+    from fovi_b200.coords import get_in_out_coords
+    from fovi_b200.knn import KNNConvLayer, KNNConvStack
+    torch.manual_seed(1)
+    ic, oc, cart = get_in_out_coords(24, 16, 1.0, 2, auto_match_cart_resources=0)
+    _, oc2, _ = get_in_out_coords(oc.resolution, 16, 1.0, 1, auto_match_cart_resources=0)
+    layers = [KNNConvLayer(3, 16, 25, ic, oc, device="cuda", ref_frame_side_length=5, bias=True),
+              KNNConvLayer(16, 32, 9, oc, oc2, device="cuda", ref_frame_side_length=3, bias=True),
+              KNNConvLayer(32, 64, 9, oc2, oc2, device="cuda", ref_frame_side_length=3, bias=False)]
+    stack = KNNConvStack(layers)
+    x = torch.randn(6, 3, ic.shape[0], device="cuda")
+    gy = torch.randn(6, 64, oc2.shape[0], device="cuda")
+
+    y = stack(x)
+    assert y.requires_grad and y.shape == gy.shape
+    y.backward(gy)
+    got = [p.grad.clone() for p in stack.parameters()]
+    for p in stack.parameters():
+        p.grad = None
+    h = x
+    for i, L in enumerate(layers):
+        h = L(h if i == 0 else h.to(torch.bfloat16))
+        if i < 2:
+            h = torch.relu(h)
+    assert rel_l2(y.detach().float().cpu().numpy(), h.detach().float().cpu().numpy()) < 1e-2
+    h.float().backward(gy)
+    for a, p in zip(got, stack.parameters()):
+        assert rel_l2(a.float().cpu().numpy(), p.grad.float().cpu().numpy()) < 3e-2
+    with torch.no_grad():
+        y2 = stack(x)
+    assert not y2.requires_grad and rel_l2(y2.float().cpu().numpy(), y.detach().float().cpu().numpy()) < 1e-2
