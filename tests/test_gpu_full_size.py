@@ -1,4 +1,4 @@
-"""GPU: the BASELINE configurations at their full sizes.  The CPU oracle used here is the C restatement
+"""GPU: the benchmark configurations at their full sizes.  The CPU oracle used here is the C restatement
 (bit-exact for the sampler), fast enough to check every output of the sampler sweep and a sample of the
 rows of the KNNConv configurations; the rest is covered by size-independent properties (determinism,
 row independence = shard equivalence)."""
