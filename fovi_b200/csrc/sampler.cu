@@ -82,6 +82,10 @@ template <typename TIn, typename TOut, int MODE, int PAD, bool NC, bool STAGE, b
 __global__ void __launch_bounds__(256, 3) fovi_sample_kernel(const SampleArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   TOut* stage = reinterpret_cast<TOut*>(smem_raw);
+  // Programmatic dependent launch: once every CTA of this grid has started, a following kernel launched with the
+  // programmatic-serialization attribute (the first KNNConv) may be scheduled onto SMs as they free up and run its
+  // prologue; it still waits for this grid's completion before it reads the output.  A no-op otherwise.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int bf = blockIdx.x;  // b*F + f
   const int b = bf / a.F, f = bf - b * a.F;

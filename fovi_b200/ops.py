@@ -89,6 +89,41 @@ def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=No
     return out
 
 
+def group_tables(idx, tap, n_in, G, max_list=256):
+    """Tables of a grouped plan.  idx [K, n_out] int (pad == n_in), tap [n_out, K]; n_out a multiple of G.
+    Returns (union lists int32 [Kq, n_out/G] padded with n_in, tap table uint16 [n_out/G, Kq] holding each entry's own
+    position, member taps uint16 [n_out/G, Kq, G] with 0xFFFF where the entry is not a neighbour of that member), or
+    None when a union list would exceed `max_list` entries or a member lists a point twice."""
+    idx = np.asarray(idx)
+    tap = np.asarray(tap)
+    K, n_out = idx.shape
+    ng = n_out // G
+    cols = idx.T.reshape(ng, G * K).astype(np.int64)               # members' lists side by side
+    taps = tap.reshape(ng, G * K).astype(np.int64)
+    member = np.repeat(np.arange(G), K)[None, :].repeat(ng, 0)
+    order = np.argsort(cols, axis=1, kind="stable")
+    sc = np.take_along_axis(cols, order, 1)
+    mem = np.take_along_axis(member, order, 1)
+    first = np.ones_like(sc, dtype=bool)
+    first[:, 1:] = sc[:, 1:] != sc[:, :-1]
+    first &= sc != n_in                                              # pad entries join no list
+    if ((sc[:, 1:] == sc[:, :-1]) & (mem[:, 1:] == mem[:, :-1]) & (sc[:, 1:] != n_in)).any():
+        return None
+    pos = np.cumsum(first, 1) - 1                                    # position of each entry's point in the union list
+    ku = int(first.sum(1).max()) if first.size else 0
+    if ku > max_list or ku == 0:
+        return None
+    kq = -(-ku // 8) * 8
+    uidx = np.full((kq, ng), n_in, np.int32)
+    mtap = np.full((ng, kq, G), 0xFFFF, np.uint16)
+    rows = np.arange(ng)[:, None].repeat(G * K, 1)
+    valid = sc != n_in
+    uidx[pos[valid], rows[valid]] = sc[valid]
+    mtap[rows[valid], pos[valid], mem[valid]] = np.take_along_axis(taps, order, 1)[valid]
+    utap = np.ascontiguousarray(np.arange(kq, dtype=np.uint16)[None, :].repeat(ng, 0))
+    return np.ascontiguousarray(uidx), utap, np.ascontiguousarray(mtap)
+
+
 class KnnConvPlan:
     """Device copy of one layer's compacted neighbour/tap tables (fovi_knnconv_plan)."""
 
@@ -120,39 +155,17 @@ class KnnConvPlan:
         """A second plan whose "points" are groups of G consecutive output points (G*c_out channels side by side) and whose
         neighbour lists are the unions of the members' lists: with 3-4 input channels an MMA over one point's 64-96 output
         channels costs as much to issue as one over 256, and consecutive points share most of their neighbours."""
-        n_in, n_out, K = self.n_in, self.n_out, self.K
         for G in candidates:
-            if G < 2 or n_out % G or G * self.c_out > 256:
+            if G < 2 or self.n_out % G or G * self.c_out > 256:
                 continue
-            ng = n_out // G
-            cols = idx.T.reshape(ng, G * K).astype(np.int64)               # members' lists side by side
-            taps = tp.reshape(ng, G * K).astype(np.int64)
-            member = np.repeat(np.arange(G), K)[None, :].repeat(ng, 0)
-            order = np.argsort(cols, axis=1, kind="stable")
-            sc = np.take_along_axis(cols, order, 1)
-            first = np.ones_like(sc, dtype=bool)
-            first[:, 1:] = sc[:, 1:] != sc[:, :-1]
-            first &= sc != n_in                                              # pad entries join no list
-            pos = np.cumsum(first, 1) - 1                                    # position of each entry's point in the union list
-            mem = np.take_along_axis(member, order, 1)
-            dup = (sc[:, 1:] == sc[:, :-1]) & (mem[:, 1:] == mem[:, :-1]) & (sc[:, 1:] != n_in)
-            if dup.any():                                                    # a member lists a point twice: leave the layer ungrouped
-                return
-            ku = int(first.sum(1).max())
-            if ku > 256 or ku >= 0xFFFF:
+            tables = group_tables(idx, tp, self.n_in, G)
+            if tables is None:
                 continue
-            kq = -(-ku // 8) * 8
-            uidx = np.full((kq, ng), n_in, np.int32)
-            mtap = np.full((ng, kq, G), 0xFFFF, np.uint16)
-            rows = np.arange(ng)[:, None].repeat(G * K, 1)
-            valid = sc != n_in
-            uidx[pos[valid], rows[valid]] = sc[valid]
-            mtap[rows[valid], pos[valid], mem[valid]] = np.take_along_axis(taps, order, 1)[valid]
-            utap = np.ascontiguousarray(np.arange(kq, dtype=np.uint16)[None, :].repeat(ng, 0))   # tap = position in the union list
+            uidx, utap, mtap = tables
+            kq, ng = uidx.shape
             hg = C.c_void_p()
-            uidx = np.ascontiguousarray(uidx)
             with torch.cuda.device(self.device):
-                check(lib.fovi_knnconv_plan_create(uidx.ctypes.data_as(C.c_void_p), utap.ctypes.data_as(C.c_void_p), n_in, ng, kq, kq,
+                check(lib.fovi_knnconv_plan_create(uidx.ctypes.data_as(C.c_void_p), utap.ctypes.data_as(C.c_void_p), self.n_in, ng, kq, kq,
                                                    self.c_in, G * self.c_out, C.byref(hg)), "fovi_knnconv_plan_create")
             if not lib.fovi_knnconv_tc_supported(hg):
                 lib.fovi_knnconv_plan_destroy(hg)

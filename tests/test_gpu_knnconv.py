@@ -183,3 +183,25 @@ def test_shapes_outside_the_tensor_core_path(ops):
         plan.pack_weights(dev(w))
     y = plan.forward_f32(dev(x), plan.pack_weights(dev(w), dtype=torch.float32)).cpu().numpy()
     assert rel_max(y, oracle.knnconv_forward_closed_form(x, idx, tap.astype(np.int64), V, w)) < F32_TOL
+
+
+def test_grouped_first_layer_equals_ungrouped(ops, golden):
+    """c_in <= 4: consecutive output points sharing an accumulator (the default when a group size divides n_out) give the
+    ungrouped kernel's result up to the order of float32 accumulation."""
+    g = golden("config1.npz")
+    V, n_in = int(g["V"]), int(g["n_in"])                             # n_out = 3975 = 3 * 5^2 * 53
+    x = dev(g["sampled"])
+    for c_out, groups in ((64, {None: 3, 1: 1, 5: 1}), (48, {None: 3, 1: 1, 5: 5})):      # 5 * 64 channels exceed one accumulator
+        w = kaiming_weight(np.random.RandomState(1), c_out, 3, V)
+        bias = np.linspace(-1, 1, c_out).astype(f32)
+        outs = {}
+        for group, expect in groups.items():
+            plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], n_in, V, 3, c_out, group=group)
+            assert plan.group == expect
+            xp = ops.pack_points(x, plan)
+            outs[group] = plan.forward(xp, plan.pack_weights(dev(w)), dev(bias), relu=True, out_dtype=torch.float32, batch=8).cpu().numpy()
+            plan.check()
+        assert rel_l2(outs[None], outs[1]) < 1e-5 and rel_l2(outs[5], outs[1]) < 1e-5
+        if c_out == 64:
+            ref = np.maximum(g["conv_out_b0"] + bias[:, None], 0)
+            assert rel_l2(outs[None][0].T, ref) < BF16_TOL

@@ -135,3 +135,29 @@ def test_policy_draws_reference_fixations(golden, name, kw, train):
     assert np.array_equal(fix, g[f"{name}_fixations"])
     assert np.array_equal(size, g[f"{name}_sizes"])
     assert nxt == float(g[f"{name}_next_random"])
+
+
+def test_group_tables_are_the_union_of_the_members_lists(golden):
+    """Grouped first-layer plans: G consecutive output points share one neighbour list (the union) and keep their own taps."""
+    from fovi_b200.ops import group_tables
+    t = golden("config3_tables.npz")
+    c1 = golden("config1.npz")
+    for idx, tap, n_in, G in ((t["l0_knn_idx_pad"], t["l0_tap"], int(t["l0_n_in"]), 3), (c1["knn_idx_pad"], c1["tap"], int(c1["n_in"]), 5)):
+        K, n_out = idx.shape
+        uidx, utap, mtap = group_tables(idx, tap, n_in, G)
+        kq, ng = uidx.shape
+        assert ng == n_out // G and kq % 8 == 0 and utap.shape == (ng, kq) and mtap.shape == (ng, kq, G)
+        assert np.array_equal(utap[0], np.arange(kq))
+        for g in (0, ng // 2, ng - 1):
+            for j in range(G):
+                n = g * G + j
+                want = {int(m): int(tap[n, k]) for k, m in enumerate(idx[:, n]) if m != n_in}
+                got = {int(uidx[k, g]): int(mtap[g, k, j]) for k in range(kq) if uidx[k, g] != n_in and mtap[g, k, j] != 0xFFFF}
+                assert want == got
+            members = set(int(m) for m in uidx[:, g] if m != n_in)
+            assert len(members) == int((uidx[:, g] != n_in).sum())                      # no point twice
+    idx, tap, n_in = t["l0_knn_idx_pad"], t["l0_tap"], int(t["l0_n_in"])
+    assert group_tables(idx, tap, n_in, 11) is None                                       # union longer than the kernel's lists
+    dup = idx.copy()
+    dup[1, 0] = dup[0, 0]
+    assert group_tables(dup, tap, n_in, 3) is None                                        # a member lists a point twice
