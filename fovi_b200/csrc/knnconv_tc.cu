@@ -66,7 +66,7 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.nstage; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&hdr->acc_full[i]), 1); mbar_init(smem_u32(&hdr->acc_empty[i]), 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&hdr->acc_full[i]), 1); mbar_init(smem_u32(&hdr->acc_empty[i]), 4); }
     mbar_init(smem_u32(&hdr->drain), 1);
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -338,7 +338,8 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&hdr->acc_empty[acc]));
+      __syncwarp();   // every lane has finished reading the accumulator; one arrival per epilogue warp
+      if (lane == 0) mbar_arrive(smem_u32(&hdr->acc_empty[acc]));
       if (++acc == 2) { acc = 0; aph ^= 1u; }
       cnt = cnt_next;
     }

@@ -90,7 +90,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.nstage; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&hdr->acc_full[i]), 1); mbar_init(smem_u32(&hdr->acc_empty[i]), 256); }
+    for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&hdr->acc_full[i]), 1); mbar_init(smem_u32(&hdr->acc_empty[i]), 8); }
     mbar_init(smem_u32(&hdr->drain), 1);
     hdr->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -273,7 +273,8 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         }
       }
       tc_fence_before();
-      mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[acc]), 0));   // the leader's MMA thread waits for all 256
+      __syncwarp();   // every lane has finished reading the accumulator; one arrival per warp (8 in the pair)
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&hdr->acc_empty[acc]), 0));   // the leader's MMA thread waits for all 8
       if (++acc == 2) { acc = 0; aph ^= 1u; }
       cnt = cnt_next;
     }
