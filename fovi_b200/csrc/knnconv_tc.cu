@@ -62,7 +62,8 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t b_stage_off = A_STAGE_BYTES;
   constexpr bool C64 = MODE == MODE_C64;
-  const int chunks = C64 ? a.cp / 64 : (MODE == MODE_PAIRS ? 1 : a.cp / 8);  // operand boxes per list entry
+  // operand boxes per list entry; a last 64-channel box that reaches past cp is zero-filled by the tensor copy
+  const int chunks = C64 ? (a.cp + 63) / 64 : (MODE == MODE_PAIRS ? 1 : a.cp / 8);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.nstage; ++s) { mbar_init(smem_u32(&hdr->full[s]), 1); mbar_init(smem_u32(&hdr->empty[s]), 1); }
@@ -174,40 +175,48 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           s += done;
           if (s >= (uint32_t)a.nstage) { s -= (uint32_t)a.nstage; ph ^= 1u; }
         }
+      } else if (MODE == MODE_C8) {
+        // Eight 16-byte-row boxes of each operand per stage: lanes 0-7 issue the activation boxes, lanes 8-15 the weight
+        // boxes, all with one instruction (a single thread would pay the issue cost of sixteen tensor copies in sequence).
+        const int boxes = cnt * chunks;
+        const int steps = (boxes + 7) / 8;
+        const int j = lane & 7;
+        const bool is_b = lane >= 8;
+        for (int st = 0; st < steps; ++st) {
+          const uint32_t full = smem_u32(&hdr->full[s]);
+          bool mine = true;
+          if (lane == 0) {
+            mine = mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit);
+            if (mine) mbar_expect_tx(full, a.stage_bytes);
+          }
+          ok = __all_sync(0xffffffffu, mine);
+          if (!ok) break;
+          if (lane < 16) {
+            const int b = st * 8 + j;
+            const int k = b / chunks, cc = b - k * chunks;
+            const bool live = k < cnt;                       // boxes past the list read the zero row / tap 0
+            const uint32_t sa = stages0 + s * a.stage_bytes;
+            const uint32_t dst = is_b ? sa + b_stage_off + j * (uint32_t)a.ct * 16u : sa + j * 2048u;
+            const int c1 = is_b ? o0 : (live ? tb_idx[k] : a.n_in);
+            const int c2 = is_b ? (live ? (int)tb_tap[k] : 0) : m0;
+            tma_load_3d(dst, is_b ? &tmB : &tmA, full, cc * 8, c1, c2);
+          }
+          ++issued;
+          if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
+        }
       } else if (lane == 0) {
-        if (C64) {
-          const int steps = cnt * chunks;
-          int k = 0, cc = 0;
-          for (int st = 0; st < steps; ++st) {
-            const uint32_t full = smem_u32(&hdr->full[s]);
-            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit)) { ok = false; break; }
-            mbar_expect_tx(full, a.stage_bytes);
-            const uint32_t sa = stages0 + s * a.stage_bytes;
-            tma_load_3d(sa, &tmA, full, cc * 64, tb_idx[k], m0);
-            tma_load_3d(sa + b_stage_off, &tmB, full, cc * 64, o0, tb_tap[k]);
-            ++issued;
-            if (++cc == chunks) { cc = 0; ++k; }
-            if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
-          }
-        } else {
-          const int boxes = cnt * chunks;
-          const int steps = (boxes + 7) / 8;
-          int k = 0, cc = 0;
-          for (int st = 0; st < steps; ++st) {
-            const uint32_t full = smem_u32(&hdr->full[s]);
-            if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit)) { ok = false; break; }
-            mbar_expect_tx(full, a.stage_bytes);
-            const uint32_t sa = stages0 + s * a.stage_bytes;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const bool live = k < cnt;
-              tma_load_3d(sa + j * 2048u, &tmA, full, cc * 8, live ? tb_idx[k] : a.n_in, m0);
-              tma_load_3d(sa + b_stage_off + j * (uint32_t)a.ct * 16u, &tmB, full, cc * 8, o0, live ? tb_tap[k] : 0);
-              if (++cc == chunks) { cc = 0; ++k; }
-            }
-            ++issued;
-            if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
-          }
+        const int steps = cnt * chunks;
+        int k = 0, cc = 0;
+        for (int st = 0; st < steps; ++st) {
+          const uint32_t full = smem_u32(&hdr->full[s]);
+          if (!mbar_wait(smem_u32(&hdr->empty[s]), ph ^ 1u, abort_flag, a.status, 1, a.wait_limit)) { ok = false; break; }
+          mbar_expect_tx(full, a.stage_bytes);
+          const uint32_t sa = stages0 + s * a.stage_bytes;
+          tma_load_3d(sa, &tmA, full, cc * 64, tb_idx[k], m0);
+          tma_load_3d(sa + b_stage_off, &tmB, full, cc * 64, o0, tb_tap[k]);
+          ++issued;
+          if (++cc == chunks) { cc = 0; ++k; }
+          if (++s == (uint32_t)a.nstage) { s = 0; ph ^= 1u; }
         }
       }
       if (MODE != MODE_PAIRS) {  // lane 0 carried the ring position and the outcome
@@ -401,7 +410,11 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   const int ct = p->ct;
   if (!ct) return FOVI_ERR_UNSUPPORTED;
   const int cp = p->cin_packed;
-  const bool c64 = cp % 64 == 0 && p->x_layout != FOVI_X_PAIRS;
+  // 64-channel swizzled boxes for every layer of at least 64 channels: when cp is not a multiple of 64 the last box of a
+  // neighbour reads past the tensor's channel extent and the copy fills those columns with zeros (96 channels: two boxes,
+  // 1.33x the MMA work, against 1.7 us per stage for the same layer in 16-byte-row boxes).  FOVI_B200_C8 keeps the old rule.
+  static const bool c8_rule = getenv("FOVI_B200_C8") != nullptr;
+  const bool c64 = (c8_rule ? cp % 64 == 0 : cp >= 64) && p->x_layout != FOVI_X_PAIRS;
   // 64-channel layers with more than one batch tile run on CTA pairs (half the weight traffic per SM);
   // FOVI_B200_SINGLE_CTA=1 keeps the single-CTA kernel (for comparison runs).
   static const bool single_only = getenv("FOVI_B200_SINGLE_CTA") != nullptr;

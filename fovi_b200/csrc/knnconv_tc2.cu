@@ -85,7 +85,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();      // 0 = leader (issues the MMAs), 1 = peer
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-  const int chunks = a.cp / 64;
+  const int chunks = (a.cp + 63) / 64;   // a last box reaching past cp is zero-filled by the tensor copy
   const int half = a.ct / 2;                    // rows of B this CTA stages
 
   if (threadIdx.x == 0) {
@@ -294,7 +294,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype,
                                  int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit) {
   const int ct = p->ct, cp = p->cin_packed;
-  if (p->x_layout != FOVI_X_BNC || cp % 64 || !ct || ct % 32 || ct < 32 || B <= BM) return FOVI_ERR_UNSUPPORTED;
+  if (p->x_layout != FOVI_X_BNC || cp < 64 || !ct || ct % 32 || ct < 32 || B <= BM) return FOVI_ERR_UNSUPPORTED;
   const int sms = fovi::sm_count();
   if (sms < 2) return FOVI_ERR_UNSUPPORTED;
   Tc2Args a;

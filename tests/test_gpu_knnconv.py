@@ -118,6 +118,9 @@ def test_config4_patch_embed(ops, golden, tag):
     (3, 128, 30, 11, 7, 16, 384),    # two channel chunks, two c_out tiles of 192
     (2, 24, 30, 11, 7, 3, 48),       # 24 channels: three 8-channel boxes per neighbour, colliding taps (V < K)
     (257, 192, 12, 5, 3, 5, 256),    # three batch tiles, widest accumulator
+    (5, 96, 40, 13, 9, 16, 64),      # 96 channels: the second 64-channel box of a neighbour is half zero-filled
+    (200, 96, 40, 13, 9, 16, 64),    # the same on CTA pairs
+    (140, 72, 25, 9, 5, 9, 32),      # 72 channels on CTA pairs
 ])
 def test_random_small_cases_vs_oracle(ops, B, Cin, Nin, Nout, K, V, Cout):
     rs = np.random.RandomState(B * 1000 + Cin)
