@@ -4,7 +4,10 @@
 // Threads are laid out along the contiguous dimension of the activations (channels for the channels-last
 // layout, points for the reference's [B,C,N]), so every neighbour read of a warp is one or two cache lines
 // (channels-last) or a short gather (points-last).  NaN inputs are skipped like pads, as nanmean/nansum do.
+#include <cstdint>
 #include <vector>
+
+#include <cuda_bf16.h>
 
 #include "common.cuh"
 
@@ -36,6 +39,43 @@ __global__ void knnpool_kernel(const T* __restrict__ X, T* __restrict__ Y, const
     }
     if (MODE == 1) acc = acc / (float)cnt;   // no valid neighbour: 0/0 = NaN, as nanmean
     Y[e] = from_float<T>(acc);
+  }
+}
+
+// Channels-last bf16 with C a multiple of 8: one thread per (row, output point, 8 channels), 16-byte loads, so a warp
+// reads up to 512 contiguous bytes per neighbour.  Same arithmetic as the scalar kernel (float32 compare / add, NaN skipped).
+template <int MODE>
+__global__ void knnpool_bnc8_kernel(const __nv_bfloat16* __restrict__ X, __nv_bfloat16* __restrict__ Y, const int* __restrict__ idx, int B,
+                                    int C, int n_in, int n_out, int K) {
+  const int c8 = C >> 3;
+  const long long total = (long long)B * n_out * c8;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int cg = (int)(e % c8);
+    const long long r = e / c8;
+    const int n = (int)(r % n_out);
+    const long long b = r / n_out;
+    const int* nb = idx + (long long)n * K;
+    const uint4* xb = reinterpret_cast<const uint4*>(X + b * (long long)n_in * C) + cg;
+    float acc[8];
+    int cnt[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { acc[i] = MODE == 0 ? -INFINITY : 0.f; cnt[i] = 0; }
+    for (int k = 0; k < K; ++k) {
+      const int j = __ldg(nb + k);
+      if (j >= n_in) continue;
+      const uint4 q = __ldg(xb + (long long)j * c8);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float lo = __uint_as_float(w[i] << 16), hi = __uint_as_float(w[i] & 0xFFFF0000u);   // bf16 -> float32, exact
+        if (lo == lo) { if (MODE == 0) acc[2 * i] = fmaxf(acc[2 * i], lo); else acc[2 * i] += lo; ++cnt[2 * i]; }
+        if (hi == hi) { if (MODE == 0) acc[2 * i + 1] = fmaxf(acc[2 * i + 1], hi); else acc[2 * i + 1] += hi; ++cnt[2 * i + 1]; }
+      }
+    }
+    __align__(16) __nv_bfloat16 out[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = __float2bfloat16_rn(MODE == 1 ? acc[i] / (float)cnt[i] : acc[i]);
+    reinterpret_cast<uint4*>(Y)[e] = *reinterpret_cast<const uint4*>(out);
   }
 }
 
@@ -79,6 +119,16 @@ extern "C" int fovi_knnpool_forward(const fovi_knnpool_plan* p, const void* X, i
   const long long total = (long long)B * C * p->n_out;
   const int grid = (int)std::min<long long>((total + 255) / 256, (long long)fovi::sm_count() * 32);
   const int bnc = layout == FOVI_ACT_BNC;
+  if (bnc && dtype == FOVI_BF16 && C % 8 == 0 && (reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) % 16 == 0) {
+    const long long tot8 = total / 8;
+    const int g8 = (int)std::min<long long>((tot8 + 255) / 256, (long long)fovi::sm_count() * 32);
+    const __nv_bfloat16* x = (const __nv_bfloat16*)X;
+    __nv_bfloat16* y = (__nv_bfloat16*)Y;
+    if (mode == 0) knnpool_bnc8_kernel<0><<<g8, 256, 0, st>>>(x, y, p->idx, B, C, p->n_in, p->n_out, p->K);
+    else if (mode == 1) knnpool_bnc8_kernel<1><<<g8, 256, 0, st>>>(x, y, p->idx, B, C, p->n_in, p->n_out, p->K);
+    else knnpool_bnc8_kernel<2><<<g8, 256, 0, st>>>(x, y, p->idx, B, C, p->n_in, p->n_out, p->K);
+    return fovi::after_launch("knnpool_bnc8_kernel");
+  }
 #define RUN(T, M) knnpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)X, (T*)Y, p->idx, B, C, p->n_in, p->n_out, p->K, bnc)
   if (dtype == FOVI_F32) { if (mode == 0) RUN(float, 0); else if (mode == 1) RUN(float, 1); else RUN(float, 2); }
   else { if (mode == 0) RUN(__nv_bfloat16, 0); else if (mode == 1) RUN(__nv_bfloat16, 1); else RUN(__nv_bfloat16, 2); }

@@ -57,3 +57,24 @@ def test_pooling_edge_cases():
     wantb = np.where(np.isnan(oracle._pool_gather(xb.float().permute(0, 2, 1).cpu().numpy(), idx)), -np.inf,
                      oracle._pool_gather(xb.float().permute(0, 2, 1).cpu().numpy(), idx)).max(2)
     assert np.array_equal(yb.float().permute(0, 2, 1).cpu().numpy(), wantb)
+
+
+@pytest.mark.parametrize("mode", ["max", "avg", "sum"])
+def test_vectorised_channels_last_kernel_equals_scalar_kernel(mode):
+    """bf16 channels-last with a multiple of 8 channels takes the 16-byte-load kernel: same numbers as the scalar one
+    (run here on float32 copies of the same bf16 values), pads and NaN inputs included."""
+    from fovi_b200 import ops
+    rs = np.random.RandomState(11)
+    B, C, Nin, Nout, K = 5, 24, 37, 19, 9
+    x = torch.from_numpy(rs.standard_normal((B, Nin, C)).astype(f32)).to(torch.bfloat16)
+    x[1, 3, 5] = float("nan")
+    x[2, :, 7] = float("nan")                                   # a channel that is NaN everywhere in one row
+    idx = rs.randint(0, Nin + 1, (K, Nout)).astype(np.int32)
+    idx[:, 0] = Nin
+    plan = ops.KnnPoolPlan(idx, Nin)
+    y = plan.forward(x.cuda(), mode, ops.ACT_BNC)
+    ref = plan.forward(x.float().cuda(), mode, ops.ACT_BNC).to(torch.bfloat16)        # scalar kernel, float32 in and out
+    assert y.dtype == torch.bfloat16 and y.shape == (B, Nout, C)
+    a, b = y.float().cpu().numpy(), ref.float().cpu().numpy()
+    assert np.array_equal(np.isnan(a), np.isnan(b))
+    assert np.array_equal(np.nan_to_num(a, nan=0.0, posinf=1e30, neginf=-1e30), np.nan_to_num(b, nan=0.0, posinf=1e30, neginf=-1e30))
