@@ -254,9 +254,14 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
             }
             if (row < a.B) {
               if (a.y_f32) {
-                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16);
+                float* dst = reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                for (int i = 0; i < 2; ++i) {
+                  uint32_t w8[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) w8[e] = __float_as_uint(v[8 * i + e]);
+                  st_global_32(dst + 8 * i, w8);
+                }
               } else {
                 uint32_t pk[8];
 #pragma unroll
@@ -264,9 +269,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
                   __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
                   pk[i] = *reinterpret_cast<uint32_t*>(&h);
                 }
-                uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.Y) + y_off + c0 + g * 16);
-                dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                st_global_32(reinterpret_cast<__nv_bfloat16*>(a.Y) + y_off + c0 + g * 16, pk);
               }
             }
           }

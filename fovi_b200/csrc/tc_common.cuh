@@ -106,6 +106,18 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// One 32-byte store (a whole sector) when the address allows it, else two 16-byte stores.
+__device__ __forceinline__ void st_global_32(void* p, const uint32_t (&w)[8]) {
+  if ((reinterpret_cast<uintptr_t>(p) & 31u) == 0) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]),
+                 "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+  } else {
+    uint4* d = reinterpret_cast<uint4*>(p);
+    d[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    d[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+}
+
 // Shared-memory matrix descriptor (K-major operand).  layout: 0 = no swizzle, 2 = 128-byte swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   uint64_t d = 0;
