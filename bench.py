@@ -28,7 +28,7 @@ sys.path.insert(0, ROOT)
 CHANS = [3, 64, 192, 384, 256, 256]
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, from one ncu capture of this workload at its default size
 # (256 images x 4 fixations; profiles/dram_traffic_bench_default.md): sampler, then the five KNNConv launches.
-NCU_DRAM_TRAFFIC_MB = {"sampler": 238.9, "conv": [213.3, 193.1, 218.5, 275.9, 200.9]}
+NCU_DRAM_TRAFFIC_MB = {"sampler": 239.5, "conv": [220.6, 197.2, 226.0, 286.3, 206.8]}
 METRIC = "images x fixations/s through sensor+KNNConv"
 UNIT = "img*fix/s"
 
