@@ -413,11 +413,13 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   const int ct = p->ct;
   if (!ct) return FOVI_ERR_UNSUPPORTED;
   const int cp = p->cin_packed;
-  // 64-channel swizzled boxes for every layer of at least 64 channels: when cp is not a multiple of 64 the last box of a
-  // neighbour reads past the tensor's channel extent and the copy fills those columns with zeros (96 channels: two boxes,
-  // 1.33x the MMA work, against 1.7 us per stage for the same layer in 16-byte-row boxes).  FOVI_B200_C8 keeps the old rule.
+  // 64-channel swizzled boxes for every layer of at least 16 channels: when cp is not a multiple of 64 the last box of a
+  // neighbour reaches past the tensor's channel extent and the copy fills those columns with zeros.  Wasted MMA columns are
+  // cheap next to 16-byte-row boxes, whose stages take 1.7 us (96 -> 256 channels, 1024 rows: 0.81 -> 0.25 ms; 16 / 32 / 48
+  // -> 64 channels: 97 / 86 / 110 -> 54 / 56 / 56 us).  FOVI_B200_C8 keeps 16-byte-row boxes for non-multiples of 64.
   static const bool c8_rule = getenv("FOVI_B200_C8") != nullptr;
-  const bool c64 = (c8_rule ? cp % 64 == 0 : cp >= 64) && p->x_layout != FOVI_X_PAIRS;
+  static const int c64_min = getenv("FOVI_B200_C64_MIN") ? atoi(getenv("FOVI_B200_C64_MIN")) : 16;
+  const bool c64 = (c8_rule ? cp % 64 == 0 : cp >= c64_min) && p->x_layout != FOVI_X_PAIRS;
   // 64-channel layers with more than one batch tile run on CTA pairs (half the weight traffic per SM);
   // FOVI_B200_SINGLE_CTA=1 keeps the single-CTA kernel (for comparison runs).
   static const bool single_only = getenv("FOVI_B200_SINGLE_CTA") != nullptr;

@@ -297,7 +297,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype,
                                  int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit) {
   const int ct = p->ct, cp = p->cin_packed;
-  if (p->x_layout != FOVI_X_BNC || cp < 64 || !ct || ct % 32 || ct < 32 || B <= BM) return FOVI_ERR_UNSUPPORTED;
+  if (p->x_layout != FOVI_X_BNC || cp < 16 || !ct || ct % 32 || ct < 32 || B <= BM) return FOVI_ERR_UNSUPPORTED;
   const int sms = fovi::sm_count();
   if (sms < 2) return FOVI_ERR_UNSUPPORTED;
   Tc2Args a;
