@@ -31,6 +31,45 @@ __global__ void batch_to_inner_kernel(const T* __restrict__ src, __nv_bfloat16* 
   }
 }
 
+// Same, 64x64 tiles with two elements per access: a warp reads 64 consecutive source elements per row and writes 64 consecutive
+// batch entries (128 bytes) per row.  Needs an even fast extent and even strides (so that pairs are aligned).
+template <typename T, bool FAST_I>
+__global__ void __launch_bounds__(256) batch_to_inner_x2_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst, int B, int I, int J,
+                                                               int Jp, int Bp, long long sb, long long si, long long sj) {
+  __shared__ __nv_bfloat16 tile[64][66];
+  const int b0 = blockIdx.x * 64, f0 = blockIdx.y * 64, slow = blockIdx.z;
+  const int F = FAST_I ? I : J;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  for (int r = ty; r < 64; r += 8) {
+    const int b = b0 + r, f = f0 + 2 * tx;
+    const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
+    float v0 = 0.f, v1 = 0.f;
+    if (b < B && f < F && j < J) {   // F is even: f + 1 < F as well
+      const T* p = src + b * sb + i * si + j * sj;
+      if (sizeof(T) == 2) {
+        const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(p);
+        v0 = __bfloat162float(q.x); v1 = __bfloat162float(q.y);
+      } else {
+        const float2 q = *reinterpret_cast<const float2*>(p);
+        v0 = q.x; v1 = q.y;
+      }
+    }
+    tile[r][2 * tx] = __float2bfloat16_rn(v0);
+    tile[r][2 * tx + 1] = __float2bfloat16_rn(v1);
+  }
+  __syncthreads();
+  const int Fd = FAST_I ? I : Jp;
+  for (int r = ty; r < 64; r += 8) {
+    const int f = f0 + r, b = b0 + 2 * tx;
+    if (f < Fd && b < Bp) {          // Bp is even
+      const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
+      __nv_bfloat162 q;
+      q.x = tile[2 * tx][r]; q.y = tile[2 * tx + 1][r];
+      *reinterpret_cast<__nv_bfloat162*>(dst + ((long long)i * Jp + j) * Bp + b) = q;
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst,
@@ -42,6 +81,18 @@ extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int
   const int fast = fast_i ? I : Jp, slow = fast_i ? Jp : I;
   if (slow > 65535 || (fast + 31) / 32 > 65535) return FOVI_ERR_UNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int F = fast_i ? I : J;
+  const size_t esz = fovi::dtype_size(dtype);
+  const bool x2 = F % 2 == 0 && Bp % 2 == 0 && sb % 2 == 0 && (fast_i ? sj : si) % 2 == 0 &&
+                  reinterpret_cast<uintptr_t>(src) % (2 * esz) == 0 && reinterpret_cast<uintptr_t>(dst) % 4 == 0 && (fast + 63) / 64 <= 65535;
+  if (x2) {
+    dim3 grid2((Bp + 63) / 64, (fast + 63) / 64, slow), block2(32, 8);
+#define RUN2(T, FI) batch_to_inner_x2_kernel<T, FI><<<grid2, block2, 0, st>>>((const T*)src, (__nv_bfloat16*)dst, B, I, J, Jp, Bp, sb, si, sj)
+    if (dtype == FOVI_F32) { if (fast_i) RUN2(float, true); else RUN2(float, false); }
+    else { if (fast_i) RUN2(__nv_bfloat16, true); else RUN2(__nv_bfloat16, false); }
+#undef RUN2
+    return fovi::after_launch("batch_to_inner_x2_kernel");
+  }
   dim3 grid((Bp + 31) / 32, (fast + 31) / 32, slow), block(32, 8);
 #define RUN(T, FI) batch_to_inner_kernel<T, FI><<<grid, block, 0, st>>>((const T*)src, (__nv_bfloat16*)dst, B, I, J, Jp, Bp, sb, si, sj)
   if (dtype == FOVI_F32) { if (fast_i) RUN(float, true); else RUN(float, false); }

@@ -144,3 +144,21 @@ def test_stack_trains_in_the_kernel_layout():
     with torch.no_grad():
         y2 = stack(x)
     assert not y2.requires_grad and rel_l2(y2.float().cpu().numpy(), y.detach().float().cpu().numpy()) < 1e-2
+
+
+@pytest.mark.parametrize("shape,perm,dtype", [
+    ((70, 225, 64), (0, 2, 1), torch.bfloat16),     # channels-last activations seen as [B, C, N]: channels fast, paired accesses
+    ((70, 64, 225), (0, 1, 2), torch.float32),      # [B, C, N] contiguous: points fast, odd extent -> scalar kernel
+    ((33, 40, 6), (0, 1, 2), torch.float32),        # small, even fast extent, float32 pairs
+    ((5, 7, 3), (0, 2, 1), torch.bfloat16),         # everything odd
+])
+def test_batch_to_inner_layouts(shape, perm, dtype):
+    from fovi_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(shape, device="cuda").to(dtype).permute(*perm)            # logical [B, I, J] with some strides
+    B, I, J = x.shape
+    bp, jp = -(-B // 64) * 64, J + 3
+    y = ops.batch_to_inner(x, jp=jp, bp=bp)
+    want = torch.zeros((I, jp, bp), dtype=torch.bfloat16, device="cuda")
+    want[:, :J, :B] = x.permute(1, 2, 0).to(torch.bfloat16)
+    assert torch.equal(y, want)
