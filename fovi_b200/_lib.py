@@ -41,6 +41,7 @@ SIGNATURES = {
                                             C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_pack_weights_grouped": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_knn_depthwise_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_column_sum": (C.c_int, [_P, C.c_int, C.c_longlong, C.c_int, _P, _P]),
     "fovi_batch_to_inner": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, _P, C.c_int, C.c_int, _P]),
     "fovi_knn_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_tap_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, _P, _P]),

@@ -1,5 +1,7 @@
 // Layout change used by the weight-gradient contraction of KNNConv: the batch index becomes the innermost
 // (contiguous) one, so that it can play the role of the channels in the tensor-core kernel.
+#include <algorithm>
+
 #include <cuda_bf16.h>
 
 #include "common.cuh"
@@ -70,7 +72,54 @@ __global__ void __launch_bounds__(256) batch_to_inner_x2_kernel(const T* __restr
   }
 }
 
+// Column sums of a row-major [R, C] matrix (C even) into float32 dst[C] (zeroed by the caller's launch order: see the entry
+// point).  A warp reads 64 consecutive columns of a row (128 bytes of bf16); rows are strided over the 8 warps of a block
+// and over grid.y; partial sums meet in shared memory and leave with one atomic per column and block.
+template <typename T>
+__global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ src, float* __restrict__ dst, long long R, int C,
+                                                        long long rows_per_block) {
+  __shared__ float part[8][64];
+  const int c = blockIdx.x * 64 + 2 * threadIdx.x;
+  const long long r0 = blockIdx.y * rows_per_block, r1 = min(R, r0 + rows_per_block);
+  float s0 = 0.f, s1 = 0.f;
+  if (c < C) {
+    for (long long r = r0 + threadIdx.y; r < r1; r += 8) {
+      const T* p = src + r * C + c;
+      if (sizeof(T) == 2) {
+        const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(p);
+        s0 += __bfloat162float(q.x); s1 += __bfloat162float(q.y);
+      } else {
+        const float2 q = *reinterpret_cast<const float2*>(p);
+        s0 += q.x; s1 += q.y;
+      }
+    }
+  }
+  part[threadIdx.y][2 * threadIdx.x] = s0;
+  part[threadIdx.y][2 * threadIdx.x + 1] = s1;
+  __syncthreads();
+  if (threadIdx.y == 0) {
+    for (int e = 0; e < 2; ++e) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += part[w][2 * threadIdx.x + e];
+      if (c + e < C) atomicAdd(dst + c + e, t);
+    }
+  }
+}
+
 }  // namespace
+
+extern "C" int fovi_column_sum(const void* src, int dtype, long long R, int C, float* dst, void* stream) {
+  if (!fovi::valid_dtype(dtype) || R < 0 || C <= 0 || !dst) return FOVI_ERR_INVALID_ARGUMENT;
+  if (C % 2 || (R > 0 && (!src || reinterpret_cast<uintptr_t>(src) % (2 * fovi::dtype_size(dtype))))) return FOVI_ERR_UNSUPPORTED;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  FOVI_CUDA(cudaMemsetAsync(dst, 0, sizeof(float) * (size_t)C, st));
+  if (R == 0) return FOVI_OK;
+  const long long rows_per_block = std::max<long long>(256, (R + 4095) / 4096);
+  dim3 grid((C + 63) / 64, (unsigned)((R + rows_per_block - 1) / rows_per_block)), block(32, 8);
+  if (dtype == FOVI_F32) column_sum_kernel<float><<<grid, block, 0, st>>>((const float*)src, dst, R, C, rows_per_block);
+  else column_sum_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)src, dst, R, C, rows_per_block);
+  return fovi::after_launch("column_sum_kernel");
+}
 
 extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst,
                                    int Jp, int Bp, void* stream) {

@@ -29,19 +29,22 @@ MAX_LIST = 256      # longest neighbour list the tensor-core kernel takes
 
 def _grouped(keys, n_groups, limit=None):
     """Stable grouping of entry indices by key.  Returns (order, group id of each ordered entry, position inside its
-    group, number of groups, owner key of each group); groups longer than `limit` are split into consecutive parts."""
+    group, number of groups, parts).  With `limit`, groups longer than it are cut into consecutive parts; `parts` is then
+    either an int P (every key has P parts, some possibly empty: part p of key g is group g*P + p) or, when that would
+    leave too many empty parts, the array of each group's owner key."""
     order = np.argsort(keys, kind="stable")
     k = keys[order]
     start = np.searchsorted(k, np.arange(n_groups))
     pos = np.arange(k.size) - start[k]
     if limit is None:
-        return order, k, pos, n_groups, np.arange(n_groups)
+        return order, k, pos, n_groups, 1
     counts = np.bincount(k, minlength=n_groups)
-    parts = np.maximum(1, -(-counts // limit))
-    first = np.concatenate([[0], np.cumsum(parts)[:-1]])
-    gid = first[k] + pos // limit
-    owner = np.repeat(np.arange(n_groups), parts)
-    return order, gid, pos % limit, int(parts.sum()), owner
+    need = np.maximum(1, -(-counts // limit))
+    P = int(need.max()) if need.size else 1
+    if n_groups * P <= 1.3 * need.sum():                    # few empty parts: uniform, the parts are summed by a reduction
+        return order, k * P + pos // limit, pos % limit, n_groups * P, P
+    first = np.concatenate([[0], np.cumsum(need)[:-1]])     # uneven lists: as many parts as each key needs, summed by index
+    return order, first[k] + pos // limit, pos % limit, int(need.sum()), np.repeat(np.arange(n_groups), need)
 
 
 class KnnConvGrad:
@@ -88,7 +91,7 @@ class KnnConvGrad:
         if bp not in self._dw_plans:
             # Lists are cut so that there are a few hundred of them (several per SM pair), whatever the number of taps.
             limit = int(min(MAX_LIST, max(8, -(-self._v.size // 300 // 8) * 8)))
-            order, gid, pos, n_groups, owner = _grouped(self._v, self.V, limit)
+            order, gid, pos, n_groups, parts = _grouped(self._v, self.V, limit)
             kw = max(8, int(pos.max()) + 1 if pos.size else 8)
             idx_w = np.full((kw, n_groups), self.n_out, np.int32)
             tap_w = np.zeros((n_groups, kw), np.uint16)
@@ -97,7 +100,7 @@ class KnnConvGrad:
             plan = ops.KnnConvPlan(idx_w, tap_w, self.n_out, self.n_in, bp, self.c_in_pad, device=self.device)
             if not plan.tc_supported:
                 raise NotImplementedError("the weight-gradient contraction is outside the tensor-core kernel's shapes")
-            self._dw_plans[bp] = (plan, torch.from_numpy(owner).to(self.device))
+            self._dw_plans[bp] = (plan, parts if isinstance(parts, int) else torch.from_numpy(parts).to(self.device))
         return self._dw_plans[bp]
 
     # ---- dW of a layer with at most 4 input channels
@@ -152,12 +155,15 @@ class KnnConvGrad:
             return self._weight_grad_few(gy, x)
         B = gy.shape[0]
         bp = -(-B // 64) * 64
-        plan, owner = self.dw_plan(bp)
+        plan, parts_per_tap = self.dw_plan(bp)
         gy_t = ops.batch_to_inner(gy, bp=bp)                                           # [c_out, n_out, bp]
         x_t = ops.batch_to_inner(x.permute(0, 2, 1), jp=self.c_in_pad, bp=bp)          # [n_in, c_in_pad, bp]
-        parts = plan.forward(gy_t, x_t, out_dtype=torch.float32)                # [c_out, groups, c_in_pad]
-        dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
-        dw.index_add_(1, owner, parts)
+        parts = plan.forward(gy_t, x_t, out_dtype=torch.float32)                # [c_out, V * parts_per_tap, c_in_pad]
+        if isinstance(parts_per_tap, int):
+            dw = parts.view(self.c_out, self.V, parts_per_tap, self.c_in_pad).sum(2) if parts_per_tap > 1 else parts
+        else:
+            dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
+            dw.index_add_(1, parts_per_tap, parts)
         return dw[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)
 
 
@@ -218,7 +224,7 @@ class _KnnConvPointsFunction(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             gw = g.weight_grad(gy.permute(0, 2, 1), x if ctx.first else x.permute(0, 2, 1)).to(weight.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = gy.sum((0, 1), dtype=torch.float32)
+            gb = ops.column_sum(gy) if gy.shape[-1] % 2 == 0 else gy.sum((0, 1), dtype=torch.float32)
         return gx, gw, gb, None, None
 
 

@@ -387,5 +387,16 @@ def batch_to_inner(src, jp=None, bp=None, out=None):
     return out
 
 
+def column_sum(x):
+    """x [..., C] contiguous float32/bf16 CUDA tensor -> float32 [C]: the sum over all leading dimensions."""
+    _need_cuda(x)
+    x = x.contiguous()
+    Cc = x.shape[-1]
+    out = torch.empty(Cc, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.fovi_column_sum(_ptr(x), _dt(x.dtype), x.numel() // Cc, Cc, _ptr(out), _stream()), "fovi_column_sum")
+    return out
+
+
 def launch_count():
     return lib.fovi_launch_count()

@@ -246,6 +246,11 @@ int fovi_knn_depthwise_forward(const fovi_knnconv_plan* plan, const void* X, int
 int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst, int Jp,
                         int Bp, void* stream);
 
+/* Bias gradient: dst[c] = sum over the R rows of the row-major [R, C] matrix src (bf16 or float32, C even), float32
+ * accumulation; dst is overwritten.  (The reference: autograd of the bias add in F.linear, fovi/arch/knn.py:555.) */
+int fovi_column_sum(const void* src, int dtype, long long R, int C, float* dst, void* stream);
+
+
 /* ------------------------------------------------------------------------------------------
  * Table construction on the host, with a reproducible rule for ties.
  * Replaces the neighbour search _compute_euclidean_distances_batched + topk (fovi/arch/knn.py:101-152) and
