@@ -162,3 +162,15 @@ def test_batch_to_inner_layouts(shape, perm, dtype):
     want = torch.zeros((I, jp, bp), dtype=torch.bfloat16, device="cuda")
     want[:, :J, :B] = x.permute(1, 2, 0).to(torch.bfloat16)
     assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("shape,dtype", [((1000, 37, 64), torch.bfloat16), ((3, 5, 6), torch.float32), ((70000, 2), torch.float32)])
+def test_column_sum(shape, dtype):
+    from fovi_b200 import ops
+    torch.manual_seed(2)
+    x = torch.randn(shape, device="cuda").to(dtype)
+    got = ops.column_sum(x)
+    want = x.double().reshape(-1, shape[-1]).sum(0)
+    assert got.dtype == torch.float32 and got.shape == (shape[-1],)
+    scale = float(x.double().abs().reshape(-1, shape[-1]).sum(0).max())
+    assert float((got.double() - want).abs().max()) <= 1e-5 * scale
