@@ -208,3 +208,28 @@ def test_grouped_first_layer_equals_ungrouped(ops, golden):
         if c_out == 64:
             ref = np.maximum(g["conv_out_b0"] + bias[:, None], 0)
             assert rel_l2(outs[None][0].T, ref) < BF16_TOL
+
+
+def test_random_shape_sweep(ops):
+    """Twenty-four seeded random layers across the operand modes (1-4 channels, 5-8, 16-63, 64 and up with and without a
+    multiple of 64), c_out tiles, batch sizes around the 128/256-row tile edges, with and without bias / ReLU."""
+    rs = np.random.RandomState(123)
+    for it in range(24):
+        cin = int(rs.choice([1, 2, 3, 4, 5, 8, 16, 24, 40, 64, 72, 96, 128, 200]))
+        cout = int(rs.choice([16, 32, 48, 64, 96, 128, 192, 256, 320, 384]))
+        B = int(rs.choice([1, 2, 7, 127, 128, 129, 200, 255, 256, 257, 300]))
+        Nin = int(rs.randint(5, 80)); Nout = int(rs.choice([1, 2, 3, 6, 9, 12, 20, 33])); K = int(rs.randint(1, min(Nin, 30) + 1))
+        V = int(rs.randint(1, 40))
+        x = rs.standard_normal((B, cin, Nin)).astype(f32)
+        idx = np.stack([rs.choice(Nin + 1, K, replace=False) for _ in range(Nout)], 1).astype(np.int32)
+        tap = rs.randint(0, V, (Nout, K)).astype(np.uint16)
+        w = (rs.standard_normal((cout, cin * V)) / np.sqrt(cin * K)).astype(f32)
+        b = rs.standard_normal(cout).astype(f32) if rs.rand() < 0.7 else None
+        relu = bool(rs.rand() < 0.5)
+        plan = ops.KnnConvPlan(idx, tap, Nin, V, cin, cout)
+        assert plan.tc_supported
+        ref = oracle.knnconv_forward_closed_form(bf16_round(x), idx, tap.astype(np.int64), V, bf16_round(w), b, relu=relu)
+        for od, tol in ((torch.float32, 2e-3), (torch.bfloat16, 1e-2)):
+            y = run_tc(ops, plan, x, w, b, relu=relu, out_dtype=od)
+            err = np.abs(y - ref).max()
+            assert err < tol * max(1.0, np.abs(ref).max()), (it, cin, cout, B, Nin, Nout, K, V, plan.group, od, err)
