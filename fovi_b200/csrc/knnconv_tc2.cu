@@ -243,14 +243,26 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
         tc_ld32(t_base + c0, r);
         if (w == 64) tc_ld32(t_base + c0 + 32, r + 32);
         tc_ld_wait();
+        if (cnt <= 0) {   // a point without neighbours: nothing was accumulated, the columns hold an earlier item's values
+#pragma unroll
+          for (int i = 0; i < 64; ++i) r[i] = 0u;
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           if (g * 16 < w) {
             float v[16];
+            const float4* b4 = reinterpret_cast<const float4*>(bias_s + o0 + c0 + g * 16);   // 64-byte aligned
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const float x = (cnt > 0 ? __uint_as_float(r[g * 16 + i]) : 0.f) + bias_s[o0 + c0 + g * 16 + i];
-              v[i] = a.relu ? fmaxf(x, 0.f) : x;
+            for (int i = 0; i < 4; ++i) {
+              const float4 bb = b4[i];
+              v[4 * i] = __uint_as_float(r[g * 16 + 4 * i]) + bb.x;
+              v[4 * i + 1] = __uint_as_float(r[g * 16 + 4 * i + 1]) + bb.y;
+              v[4 * i + 2] = __uint_as_float(r[g * 16 + 4 * i + 2]) + bb.z;
+              v[4 * i + 3] = __uint_as_float(r[g * 16 + 4 * i + 3]) + bb.w;
+            }
+            if (a.relu) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
             }
             if (row < a.B) {
               if (a.y_f32) {
