@@ -21,6 +21,7 @@ SIGNATURES = {
     "fovi_sampler_plan_num_points": (C.c_int, [_P]),
     "fovi_sample_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), _P, _P,
                                       C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_sampler_check": (C.c_int, [_P, _P]),
     "fovi_knnconv_plan_create": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
     "fovi_knnconv_plan_destroy": (None, [_P]),
     "fovi_knnconv_cin_packed": (C.c_int, [_P]),

@@ -38,9 +38,21 @@
 // Every wait is bounded: a wait that gives up raises a CTA-wide abort flag and a status word in
 // global memory (read back by fovi_knnconv_check); all roles then drain and leave normally, the
 // tensor memory is freed and the context stays usable.
-#include <stdlib.h>
-
 #include "tc_common.cuh"
+
+// Tuning constants (compile-time; a comparison build overrides them with -D).
+#ifndef FOVI_TC_C64_MIN
+#define FOVI_TC_C64_MIN 16          // packed channel count from which 64-channel swizzled boxes are used
+#endif
+#ifndef FOVI_TC_SINGLE_CTA_ONLY
+#define FOVI_TC_SINGLE_CTA_ONLY 0   // 1: never use the CTA-pair kernel
+#endif
+#ifndef FOVI_TC_PAIR_CTAS
+#define FOVI_TC_PAIR_CTAS 3         // pair mode: CTAs per SM at most
+#endif
+#ifndef FOVI_TC_PAIR_GROUPS
+#define FOVI_TC_PAIR_GROUPS 2       // pair mode: stages the producer warp fills per pass
+#endif
 
 namespace {
 
@@ -428,14 +440,10 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   // 64-channel swizzled boxes for every layer of at least 16 channels: when cp is not a multiple of 64 the last box of a
   // neighbour reaches past the tensor's channel extent and the copy fills those columns with zeros.  Wasted MMA columns are
   // cheap next to 16-byte-row boxes, whose stages take 1.7 us (96 -> 256 channels, 1024 rows: 0.81 -> 0.25 ms; 16 / 32 / 48
-  // -> 64 channels: 97 / 86 / 110 -> 54 / 56 / 56 us).  FOVI_B200_C8 keeps 16-byte-row boxes for non-multiples of 64.
-  static const bool c8_rule = getenv("FOVI_B200_C8") != nullptr;
-  static const int c64_min = getenv("FOVI_B200_C64_MIN") ? atoi(getenv("FOVI_B200_C64_MIN")) : 16;
-  const bool c64 = (c8_rule ? cp % 64 == 0 : cp >= c64_min) && p->x_layout != FOVI_X_PAIRS;
-  // 64-channel layers with more than one batch tile run on CTA pairs (half the weight traffic per SM);
-  // FOVI_B200_SINGLE_CTA=1 keeps the single-CTA kernel (for comparison runs).
-  static const bool single_only = getenv("FOVI_B200_SINGLE_CTA") != nullptr;
-  if (c64 && !single_only && B > BM && ct % 32 == 0) {
+  // -> 64 channels: 97 / 86 / 110 -> 54 / 56 / 56 us).
+  const bool c64 = cp >= FOVI_TC_C64_MIN && p->x_layout != FOVI_X_PAIRS;
+  // 64-channel layers with more than one batch tile run on CTA pairs (half the weight traffic per SM).
+  if (c64 && !FOVI_TC_SINGLE_CTA_ONLY && B > BM && ct % 32 == 0) {
     const int rc2 = fovi::launch_knnconv_tc_pair(p, X, Wt, bias, Y, y_dtype, B, relu, reinterpret_cast<cudaStream_t>(stream), skip_loads, wait_limit);
     if (rc2 != FOVI_ERR_UNSUPPORTED) return rc2;
   }
@@ -448,7 +456,7 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
   a.wait_limit = wait_limit; a.skip_loads = skip_loads;
-  a.mt_fastest = (pairs && !getenv("FOVI_B200_POINT_FASTEST")) ? 1 : 0;
+  a.mt_fastest = pairs ? 1 : 0;
   const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
   if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;
@@ -460,14 +468,13 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   a.tmem_cols = 2 * a.acc_cols;
   // Pair mode with a narrow c_out tile is bound by per-item latencies (copy issue, short neighbour lists, small MMAs),
   // not by bandwidth: up to three CTAs per SM, each with fewer stages and a share of the tensor memory, overlap them
-  // (measured on the 3->64 first layer: 0.29 / 0.17 / 0.16 ms with 1 / 2 / 3 CTAs per SM).  FOVI_B200_PAIR_CTAS overrides.
-  static const int pair_ctas = getenv("FOVI_B200_PAIR_CTAS") ? atoi(getenv("FOVI_B200_PAIR_CTAS")) : 3;
+  // (measured on the 3->64 first layer: 0.29 / 0.17 / 0.16 ms with 1 / 2 / 3 CTAs per SM).
+  constexpr int pair_ctas = FOVI_TC_PAIR_CTAS;
   const int ctas_per_sm = !pairs ? 1 : (a.tmem_cols <= 128 && pair_ctas >= 3) ? 3 : (a.tmem_cols <= 256 && pair_ctas >= 2) ? 2 : 1;
   const uint32_t budget = (ctas_per_sm == 3 ? 73u : ctas_per_sm == 2 ? 110u : 220u) * 1024u - 2048u - a.table_bytes;
   a.nstage = (int)std::min<uint32_t>(MAX_STAGES, budget / a.stage_bytes);
   if (a.nstage < 2) return FOVI_ERR_UNSUPPORTED;
-  static const int pair_groups = getenv("FOVI_B200_PAIR_GROUPS") ? atoi(getenv("FOVI_B200_PAIR_GROUPS")) : 2;
-  a.pgroups = std::max(1, std::min(std::min(pair_groups, 3), a.nstage - 1));
+  a.pgroups = std::max(1, std::min(std::min(FOVI_TC_PAIR_GROUPS, 3), a.nstage - 1));
   const size_t smem = 1024 /*align slack*/ + 1024 /*header*/ + a.table_bytes + (size_t)a.nstage * a.stage_bytes;
 
   CUtensorMap tmA, tmB;

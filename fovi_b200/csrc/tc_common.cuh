@@ -161,10 +161,14 @@ __device__ __forceinline__ int item_point(const TcArgs& a, int item) {
 
 namespace fovi {
 // Launch with the programmatic-stream-serialization attribute (see the griddepcontrol note in the kernels):
-// the kernel may start while the previous kernel of the stream drains.  FOVI_B200_NO_PDL=1 launches plainly.
+// the kernel may start while the previous kernel of the stream drains.  A build with -DFOVI_TC_NO_PDL launches plainly.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args&&... args) {
-  static const bool plain = getenv("FOVI_B200_NO_PDL") != nullptr;
+#ifdef FOVI_TC_NO_PDL
+  constexpr bool plain = true;
+#else
+  constexpr bool plain = false;
+#endif
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = st;

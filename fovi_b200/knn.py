@@ -7,6 +7,8 @@ tensor-core kernel (bf16 operands, fp32 accumulation) or, with ``precision='fp32
 float32 kernel.  With gradients enabled the bf16 path is differentiable (fovi_b200/grad.py: both gradient
 contractions run on the same kernel).
 """
+import warnings
+
 import numpy as np
 import torch
 import torch.nn as nn
@@ -103,6 +105,7 @@ class KNNConvLayer(nn.Module):
                                      n_in, V, in_channels, out_channels, device=dev)
         self._packed = {}          # dtype -> (weight version, data_ptr, packed tensor)
         self._grad = None
+        self._warned_no_grad = False
 
     # ---- tables in the reference's own representation, built on demand (can be hundreds of MB)
     @property
@@ -150,6 +153,13 @@ class KNNConvLayer(nn.Module):
                 return knnconv_autograd(self, X_l)
             if X_l.requires_grad:
                 raise RuntimeError("the backward pass is built for the bf16 tensor-core path: call this layer under torch.no_grad()")
+            # Only parameters want gradients and this configuration has no backward: the result carries no grad_fn, so
+            # this layer would silently stay untrained while layers behind it learn.  Say so (once per layer).
+            if not self._warned_no_grad:
+                self._warned_no_grad = True
+                warnings.warn(f"{self.__class__.__name__}: parameters require grad but this configuration (precision={self.precision!r}, "
+                              f"tensor-core path {'available' if self._plan.tc_supported else 'unavailable'}) has no backward pass; "
+                              "the output is detached and these parameters will not be trained", RuntimeWarning, stacklevel=2)
         with torch.no_grad():
             return self._forward(X_l)
 
@@ -311,8 +321,8 @@ class KNNPartitioningPatchEmbedding(KNNPatchEmbedding):
 
 class KNNConvStack(nn.Module):
     """A chain of KNNConv layers with ReLU between them, kept in the kernels' channels-last layout from
-    end to end (the conv -> activation skeleton of fovi/arch/knnalexnet.py:109-127).  Activation buffers
-    are allocated once per batch size and reused."""
+    end to end (the conv -> activation skeleton of fovi/arch/knnalexnet.py:109-127).  Buffers between layers are
+    allocated once per batch size and reused; the returned tensor is new memory on every call."""
 
     def __init__(self, layers, final_relu=False):
         super().__init__()
@@ -320,22 +330,26 @@ class KNNConvStack(nn.Module):
         self.final_relu = final_relu
         self._acts = {}
 
-    def _act_buffers(self, rows, device, out_dtype):
-        key = (rows, str(device), out_dtype)
+    def _act_buffers(self, rows, device):
+        """Buffers of the layers between the first and the last: allocated once per batch size and reused.  The last
+        layer's output is NOT among them: it is what the caller receives, so every call gets fresh memory."""
+        key = (rows, str(device))
         if key not in self._acts:
-            n = len(self.layers)
-            self._acts[key] = [torch.empty((rows, L.plan.n_out, L.out_channels), dtype=out_dtype if i == n - 1 else torch.bfloat16, device=device)
-                               for i, L in enumerate(self.layers)]
+            self._acts[key] = [torch.empty((rows, L.plan.n_out, L.out_channels), dtype=torch.bfloat16, device=device)
+                               for L in self.layers[:-1]]
         return self._acts[key]
 
     @torch.no_grad()
-    def forward_points(self, x_points, rows, out_dtype=torch.bfloat16):
-        """x_points: the first layer's kernel layout (see KNNConvLayer.forward_points) -> [rows, n_out, C_out]."""
-        bufs = self._act_buffers(rows, x_points.device, out_dtype)
+    def forward_points(self, x_points, rows, out_dtype=torch.bfloat16, out=None):
+        """x_points: the first layer's kernel layout (see KNNConvLayer.forward_points) -> [rows, n_out, C_out].
+        `out`: optional destination of the last layer (a caller that recycles its own buffer); otherwise the result
+        is newly allocated, so results of earlier calls stay valid."""
+        bufs = self._act_buffers(rows, x_points.device)
         h = x_points
         for i, L in enumerate(self.layers):
             last = i == len(self.layers) - 1
-            h = L.forward_points(h, batch=rows, relu=(not last) or self.final_relu, out=bufs[i])
+            dst = out if last else bufs[i]
+            h = L.forward_points(h, batch=rows, relu=(not last) or self.final_relu, out_dtype=out_dtype if last else torch.bfloat16, out=dst)
         return h
 
     def forward(self, X):

@@ -1,7 +1,6 @@
 """Tensor-level wrappers over the C ABI: plans own device tables, functions take torch CUDA
 tensors, pass raw pointers and the current stream, and allocate outputs with torch."""
 import ctypes as C
-import os
 
 import numpy as np
 import torch
@@ -55,6 +54,11 @@ class SamplerPlan:
         h, self._h = getattr(self, "_h", None), None
         if h and lib is not None:          # `lib` is already gone when the interpreter is shutting down
             lib.fovi_sampler_plan_destroy(h)
+
+    def check(self):
+        """Synchronise the current stream and raise if a sampler launch gave up waiting for its image copies."""
+        with torch.cuda.device(self.device):
+            check(lib.fovi_sampler_check(self._h, _stream()), "fovi_sampler_check")
 
 
 def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=None, layout=OUT_BFCN, channel_stride=None, out=None):
@@ -129,8 +133,7 @@ class KnnConvPlan:
 
     def __init__(self, knn_idx_pad, tap, n_in, V, c_in, c_out, device=None, group=None):
         """`group`: output points per accumulator of a pair-layout (c_in <= 4) layer's tensor-core path; None picks the
-        largest of 4, 3, 2 that divides n_out and keeps group*c_out <= 256 (1 = no grouping; the environment variable
-        FOVI_B200_NO_GROUPING forces 1)."""
+        largest of 4, 3, 2 that divides n_out and keeps group*c_out <= 256 (1 = no grouping)."""
         idx = np.ascontiguousarray(np.asarray(knn_idx_pad, np.int32))
         tp = np.ascontiguousarray(np.asarray(tap, np.uint16))
         K, n_out = idx.shape
@@ -147,8 +150,8 @@ class KnnConvPlan:
         self.x_layout = lib.fovi_knnconv_x_layout(h)
         self.tc_supported = bool(lib.fovi_knnconv_tc_supported(h))
         self.n_pairs = (self.n_in + 1) // 2
-        self.group, self._hg, self._member_tap, self._bias_g = 1, None, None, None
-        if self.x_layout == X_PAIRS and self.tc_supported and group != 1 and not os.environ.get("FOVI_B200_NO_GROUPING"):
+        self.group, self._hg, self._member_tap = 1, None, None
+        if self.x_layout == X_PAIRS and self.tc_supported and group != 1:
             self._make_grouped(idx, tp, (int(group),) if group else (4, 3, 2))
 
     def _make_grouped(self, idx, tp, candidates):
@@ -180,12 +183,13 @@ class KnnConvPlan:
         return self._hg if self._hg else self._h
 
     def _tc_bias(self, bias):
+        """Bias as the tensor-core entry point wants it: a grouped plan's "channels" are the members' channels side by
+        side, so the layer's bias is repeated once per member.  Recomputed on every call (a few hundred bytes): any
+        cache keyed on the tensor's address or version would go stale when a caller passes a freshly folded temporary
+        that happens to reuse a freed address."""
         if bias is None or self.group == 1:
             return bias
-        key = (bias.data_ptr(), bias._version)
-        if self._bias_g is None or self._bias_g[0] != key:
-            self._bias_g = (key, bias.detach().float().repeat(self.group).contiguous())
-        return self._bias_g[1]
+        return bias.detach().float().repeat(self.group)
 
     def __del__(self):
         for name in ("_h", "_hg"):

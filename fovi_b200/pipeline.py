@@ -44,9 +44,9 @@ class FoveatedFrontEnd:
                                   fix=torch.empty((B, F, 2), dtype=torch.float32, device=dev), s_out=s_out, acts=acts)
         return self._slots[k]
 
-    def _run(self, img, fix, slot, fixation_size=None, between=None):
-        """Sensor + stack on device tensors into the slot's buffers.  `between(i)` is called after launch i
-        (0 = sensor, 1.. = layers): the benchmark records events there."""
+    def _run(self, img, fix, slot, fixation_size=None, between=None, out=None):
+        """Sensor + stack on device tensors into the slot's buffers (`out`: destination of the last layer instead of
+        the slot's).  `between(i)` is called after launch i (0 = sensor, 1.. = layers): the benchmark records events there."""
         B, F = fix.shape[0], fix.shape[1]
         rows = B * F
         xp, _ = self.retina.forward_points(img, fix, fixation_size, conv_plan=self.first_plan, out=slot["s_out"])
@@ -55,16 +55,22 @@ class FoveatedFrontEnd:
         h = xp
         n = len(self.stack.layers)
         for i, L in enumerate(self.stack.layers):
-            h = L.forward_points(h, batch=rows, relu=(i < n - 1) or self.stack.final_relu, out=slot["acts"][i])
+            dst = out if (out is not None and i == n - 1) else slot["acts"][i]
+            h = L.forward_points(h, batch=rows, relu=(i < n - 1) or self.stack.final_relu, out_dtype=dst.dtype, out=dst)
             if between:
                 between(i + 1)
         return h
 
     @torch.no_grad()
-    def forward(self, images, fix_loc, fixation_size=None, between=None):
-        """images [B,C,H,W] and fix_loc [B,F,2] on the device -> [F*B, n_out, C_out] (channels last)."""
-        slot = self._slot("dev", images.shape[0], fix_loc.shape[1], images.shape[1:], images.dtype)
-        return self._run(images, fix_loc, slot, fixation_size, between)
+    def forward(self, images, fix_loc, fixation_size=None, between=None, out=None):
+        """images [B,C,H,W] and fix_loc [B,F,2] on the device -> [F*B, n_out, C_out] (channels last).  The result is
+        newly allocated on every call (intermediate buffers are reused) unless the caller passes its own `out`."""
+        B, F = images.shape[0], fix_loc.shape[1]
+        slot = self._slot("dev", B, F, images.shape[1:], images.dtype)
+        if out is None:
+            last = self.stack.layers[-1]
+            out = torch.empty((B * F, last.plan.n_out, last.out_channels), dtype=self.out_dtype, device=self.device)
+        return self._run(images, fix_loc, slot, fixation_size, between, out=out)
 
     @torch.no_grad()
     def run_from_host(self, images, fix_loc, out, chunks=8, fixation_size=None):

@@ -84,9 +84,9 @@ const char* fovi_version(void);
 typedef struct fovi_sampler_plan fovi_sampler_plan;
 
 /* grid_xy: HOST [N,2] float32, the rows of GridSampler.sampling_grid[0,0] — (x, -y) of the
- * sensor's cartesian coordinates in [-1,1].  The plan keeps a spatially sorted copy on the
- * current device (points are visited in image-tile order; results are written at their
- * original index).  Synchronises the device. */
+ * sensor's cartesian coordinates in [-1,1].  The plan keeps sorted copies on the current
+ * device (points are visited in image order; results are written at their original index).
+ * Synchronises the device. */
 int fovi_sampler_plan_create(const float* grid_xy, int n_points, fovi_sampler_plan** out);
 void fovi_sampler_plan_destroy(fovi_sampler_plan* plan);
 int fovi_sampler_plan_num_points(const fovi_sampler_plan* plan);
@@ -104,6 +104,12 @@ int fovi_sampler_plan_num_points(const fovi_sampler_plan* plan);
 int fovi_sample_forward(const fovi_sampler_plan* plan, const void* img, int dtype, int B, int C, int H, int W,
                         const int64_t* img_strides, const float* fix_rc, const float* fix_hw, int F, int mode,
                         int pad, void* out, int out_dtype, int layout, int out_channel_stride, void* stream);
+
+/* Synchronises `stream` and returns FOVI_ERR_DEVICE_TIMEOUT if a sampler launch on this plan since the
+ * last check gave up on the (bounded) wait for its asynchronous image copies; clears the word.  Such a
+ * launch leaves its part of the output unwritten; nothing faults or hangs.  The reference has no
+ * counterpart (F.grid_sample has no device-side waits). */
+int fovi_sampler_check(fovi_sampler_plan* plan, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * KNNConv.

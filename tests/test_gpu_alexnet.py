@@ -70,6 +70,28 @@ def test_folded_operands_follow_parameter_updates(net):
         b.norm.running_var.div_(4.0)
 
 
+def test_reloaded_parameters_reach_the_kernel(net):
+    """Forward, load other batch-norm statistics and weights, forward again: the result is that of a block built fresh
+    with the new parameters (the first block's plan is grouped, so its bias is repeated per member on the way in)."""
+    from fovi_b200.alexnet import KNNAlexNet
+    x = torch.randn(3, 3, net.layers[0].in_coords.shape[0], device="cuda")
+    blk = net.layers[0]
+    assert blk.conv.plan.group > 1
+    y_old = blk(x).clone()
+    old_state = {k: v.clone() for k, v in net.state_dict().items()}
+    other = KNNAlexNet(n_classes=10, device="cuda", **ALEXNET_SHIPPED)
+    seed_alexnet(other, 301)
+    other.eval()
+    want = other.layers[0](x)
+    for _ in range(3):                                    # several refolds: freed temporaries get their addresses reused
+        net.load_state_dict(other.state_dict())
+        got = blk(x)
+        assert torch.equal(got, want)
+        net.load_state_dict(old_state)
+        assert torch.equal(blk(x), y_old)
+    assert not torch.equal(want, y_old)
+
+
 def test_training_mode_is_refused(net):
     net.train()
     try:

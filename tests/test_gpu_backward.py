@@ -174,3 +174,23 @@ def test_column_sum(shape, dtype):
     assert got.dtype == torch.float32 and got.shape == (shape[-1],)
     scale = float(x.double().abs().reshape(-1, shape[-1]).sum(0).max())
     assert float((got.double() - want).abs().max()) <= 1e-5 * scale
+
+
+def test_layer_without_backward_warns_instead_of_silently_detaching():
+    """precision='fp32' has no backward pass: with trainable parameters and a plain input the layer says so once."""
+    import warnings
+    from fovi_b200.coords import get_in_out_coords
+    from fovi_b200.knn import KNNConvLayer
+    ic, oc, _ = get_in_out_coords(20, 16, 1.0, 2, auto_match_cart_resources=0)
+    layer = KNNConvLayer(3, 16, 9, ic, oc, device="cuda", ref_frame_side_length=3, precision="fp32")
+    x = torch.randn(2, 3, ic.shape[0], device="cuda")
+    with pytest.warns(RuntimeWarning, match="no backward pass"):
+        y = layer(x)
+    assert y.grad_fn is None
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        layer(x)                                    # once per layer
+        with torch.no_grad():
+            layer(x)
+    with pytest.raises(RuntimeError):
+        layer(x.requires_grad_())

@@ -105,6 +105,10 @@ def test_config3_stack_module_end_to_end(golden):
     assert rel_l2(out.cpu().numpy(), acts["act4"]) < 1e-2
     out2 = stack(x)
     assert torch.equal(out, out2)
+    # value semantics: a later call with the same batch size must not overwrite an earlier result
+    keep = out.clone()
+    other = stack(torch.from_numpy(synth_images(5, (2, 3, 4010))).cuda())
+    assert out.data_ptr() != other.data_ptr() and torch.equal(out, keep) and not torch.equal(other, keep)
 
 
 def test_cpu_tensors_are_refused(golden):

@@ -127,3 +127,70 @@ def test_edge_cases(ops, golden):
     # run twice: bitwise run-to-run determinism
     a = ops.sample(plan, dev(x), dev(fix * 0 + 0.4), dev(hw)); b = ops.sample(plan, dev(x), dev(fix * 0 + 0.4), dev(hw))
     assert torch.equal(a, b)
+
+
+def _pairs_to_rows(y, rows, N):
+    """Pair layout [tiles, ceil(N/2), 128, 8] -> float32 [rows, N, 4]."""
+    t = y.to(torch.float32).cpu().numpy()
+    tiles, n_pairs = t.shape[0], t.shape[1]
+    t = t.reshape(tiles, n_pairs, 128, 2, 4).transpose(0, 2, 1, 3, 4).reshape(tiles * 128, n_pairs * 2, 4)
+    return t[:rows, :N], t[:rows, N:]
+
+
+@pytest.mark.parametrize("mode", ["bilinear", "nearest"])
+@pytest.mark.parametrize("pad", ["zeros", "border"])
+def test_strip_kernel_cases(ops, golden, mode, pad):
+    """The image-stationary kernel (x-contiguous, 16-byte-aligned rows, C <= 4): strips that do not divide the height,
+    more fixations than one pass holds, windows much smaller than the image, fixations on and beyond every edge,
+    mirrored (negative) fixation sizes, 1 / 3 / 4 channels, float32 and bf16 images — all bit-exact against the oracle."""
+    m = ops.BILINEAR if mode == "bilinear" else ops.NEAREST
+    p = ops.PAD_ZEROS if pad == "zeros" else ops.PAD_BORDER
+    grid = golden("sensor_a2p78.npz")["sampling_grid"]
+    plan = ops.SamplerPlan(grid)
+    N = grid.shape[0]
+    rs = np.random.RandomState(12)
+    cases = [
+        (2, 3, 100, 132, 3, "f32"),    # height not a multiple of the strip, 33 pieces per row
+        (1, 1, 61, 64, 19, "f32"),     # more than 16 fixations of one image, one channel
+        (2, 4, 72, 40, 2, "bf16"),     # four channels, bf16 storage
+        (1, 3, 300, 512, 5, "f32"),    # image much larger than the fixation windows
+    ]
+    for B, Cc, H, W, F, dt in cases:
+        x = synth_images(B * 7 + H, (B, Cc, H, W))
+        fix = (-0.2 + 1.4 * rs.random_sample((B, F, 2))).astype(f32)            # centres on and beyond the edges
+        hw = (24 + 100 * rs.random_sample((B, F, 2))).astype(f32)
+        fix[0, 0] = (0.5, 0.5); hw[0, 0] = (H, W)
+        if F > 1:
+            hw[0, 1] = (-float(H) / 2, float(W) / 3)                             # mirrored vertically
+        if F > 2:
+            fix[0, 2] = (5.0, 0.5)                                               # wholly below the image
+        xt = torch.from_numpy(x)
+        if dt == "bf16":
+            xt = xt.to(torch.bfloat16)
+            x = xt.to(torch.float32).numpy()
+        ref = oracle.retinal_sample(x, grid, fix, hw, mode, pad)                 # [B,F,C,N]
+        xd = xt.cuda()
+        y = ops.sample(plan, xd, dev(fix), dev(hw), mode=m, pad=p, out_dtype=torch.float32)
+        assert np.array_equal(y.cpu().numpy(), ref), (B, Cc, H, W, F, dt)
+        y = ops.sample(plan, xd, dev(fix), dev(hw), mode=m, pad=p, out_dtype=torch.float32, layout=ops.OUT_FBNC, channel_stride=Cc + 2)
+        got = y.cpu().numpy()
+        assert np.array_equal(got[..., :Cc], ref.transpose(1, 0, 3, 2)) and np.all(got[..., Cc:] == 0)
+        y = ops.sample(plan, xd, dev(fix), dev(hw), mode=m, pad=p, out_dtype=torch.bfloat16, layout=ops.OUT_BFNC, channel_stride=4)
+        ref16 = torch.from_numpy(ref).to(torch.bfloat16).to(torch.float32).numpy()
+        got = y.to(torch.float32).cpu().numpy()
+        assert np.array_equal(got[..., :Cc], ref16.transpose(0, 1, 3, 2)) and np.all(got[..., Cc:] == 0)
+        out = torch.full(((B * F + 127) // 128, (N + 1) // 2, 128, 8), 7.0, dtype=torch.bfloat16, device="cuda")
+        y = ops.sample(plan, xd, dev(fix), dev(hw), mode=m, pad=p, layout=ops.OUT_FB_PAIRS, out=out)
+        got, tail = _pairs_to_rows(y, B * F, N)
+        want = ref16.transpose(1, 0, 3, 2).reshape(B * F, N, Cc)
+        assert np.array_equal(got[..., :Cc], want) and np.all(got[..., Cc:] == 0) and np.all(tail == 0)
+    # a view whose rows are not 16-byte aligned takes the general kernel and gives the same bits
+    x = synth_images(3, (2, 3, 50, 67))
+    fix = (0.2 + 0.6 * rs.random_sample((2, 2, 2))).astype(f32); hw = np.full((2, 2, 2), 60, f32)
+    wide = dev(x)
+    ref = oracle.retinal_sample(x[..., 1:65], grid, fix, hw, mode, pad)
+    assert np.array_equal(ops.sample(plan, wide[..., 1:65], dev(fix), dev(hw), mode=m, pad=p).cpu().numpy(), ref)
+    # ... and an aligned sub-window of a wider buffer (row pitch larger than the width) stays on the strip kernel
+    x = synth_images(4, (2, 3, 50, 96))
+    ref = oracle.retinal_sample(x[..., 16:80], grid, fix, hw, mode, pad)
+    assert np.array_equal(ops.sample(plan, dev(x)[..., 16:80], dev(fix), dev(hw), mode=m, pad=p).cpu().numpy(), ref)
