@@ -7,8 +7,9 @@
   into chunks of images that flow through three streams (host->device copy, kernels, device->host copy)
   with double-buffered device memory, so PCIe transfers of neighbouring chunks overlap the kernels.
 
-Rows of the result are ordered '(f b)' (fixation-major), the order in which the reference flattens
-fixations before its network (fovi/fovinet.py:281).
+Rows of ``forward``'s result are ordered '(f b)' (fixation-major), the order in which the reference flattens
+fixations before its network (fovi/fovinet.py:281); ``run_from_host`` writes ``[B, F, n_out, C_out]`` (the
+fixations of an image together), so that a chunk of images is one contiguous block of the host buffer.
 """
 import torch
 
@@ -44,12 +45,12 @@ class FoveatedFrontEnd:
                                   fix=torch.empty((B, F, 2), dtype=torch.float32, device=dev), s_out=s_out, acts=acts)
         return self._slots[k]
 
-    def _run(self, img, fix, slot, fixation_size=None, between=None, out=None):
+    def _run(self, img, fix, slot, fixation_size=None, between=None, out=None, row_order="fb"):
         """Sensor + stack on device tensors into the slot's buffers (`out`: destination of the last layer instead of
         the slot's).  `between(i)` is called after launch i (0 = sensor, 1.. = layers): the benchmark records events there."""
         B, F = fix.shape[0], fix.shape[1]
         rows = B * F
-        xp, _ = self.retina.forward_points(img, fix, fixation_size, conv_plan=self.first_plan, out=slot["s_out"])
+        xp, _ = self.retina.forward_points(img, fix, fixation_size, conv_plan=self.first_plan, out=slot["s_out"], row_order=row_order)
         if between:
             between(0)
         h = xp
@@ -73,10 +74,14 @@ class FoveatedFrontEnd:
         return self._run(images, fix_loc, slot, fixation_size, between, out=out)
 
     @torch.no_grad()
-    def run_from_host(self, images, fix_loc, out, chunks=8, fixation_size=None):
-        """images [B,C,H,W], fix_loc [B,F,2] float32, out [F,B,n_out,C_out]: PINNED host tensors.  Returns
-        after the last byte of `out` has been written."""
+    def run_from_host(self, images, fix_loc, out, chunks=8, fixation_size=None, kernels=True):
+        """images [B,C,H,W] (float32 or bfloat16), fix_loc [B,F,2] float32, out [B,F,n_out,C_out]: PINNED host tensors.
+        Returns after the last byte of `out` has been written.  Per chunk of images: one host->device copy of the images
+        (and one of the fixations), the kernels, one device->host copy of the chunk's result.
+        `kernels=False` runs the copies alone (same chunks, same streams, same dependencies): the transfer floor of
+        this pipeline on the machine at hand."""
         B, F = images.shape[0], fix_loc.shape[1]
+        assert out.shape[0] == B and out.shape[1] == F, "out is [B, F, n_out, C_out]"
         chunks = max(1, min(chunks, B))
         bounds = [(c * B) // chunks for c in range(chunks + 1)]
         if self._streams is None:
@@ -99,13 +104,14 @@ class FoveatedFrontEnd:
                 s_run.wait_event(ev_in[c])
                 if c >= 2:
                     s_run.wait_event(ev_out[c - 2])         # this slot's output has left for the host
-                y = self._run(slot["img"], slot["fix"], slot, fixation_size)
+                if kernels:
+                    y = self._run(slot["img"], slot["fix"], slot, fixation_size, row_order="bf")
+                else:
+                    y = slot["acts"][-1]
                 ev_run[c] = s_run.record_event()
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_run[c])
-                yv = y.view(F, hi - lo, y.shape[1], y.shape[2])
-                for f in range(F):
-                    out[f, lo:hi].copy_(yv[f], non_blocking=True)
+                out[lo:hi].copy_(y.view(hi - lo, F, y.shape[1], y.shape[2]), non_blocking=True)   # rows (b f): one block
                 ev_out[c] = s_out.record_event()
         for s in self._streams:
             cur.wait_stream(s)

@@ -107,6 +107,10 @@ class GridSampler(nn.Module):
             raise NotImplementedError("return_coords: the normalised grid is not materialised by the CUDA sampler")
         return out
 
+    def check(self):
+        """Synchronise the current stream and raise if a launch of this sampler gave up on its bounded wait."""
+        self._plan.check()
+
     def all_coords(self, device=None):
         return self.coords.cartesian.to(self.device if device is None else device)
 
@@ -161,10 +165,13 @@ class RetinalTransform(nn.Module):
         return self.sampler(x, fix_loc=fix_loc, fixation_size=fixation_size).to(self.dtype)
 
     @torch.no_grad()
-    def forward_points(self, x, fix_loc, fixation_size=None, conv_plan=None, out=None):
-        """All fixations sampled straight into the layout the first KNNConv consumes (rows ordered
-        '(f b)' as fovi/fovinet.py:281 flattens them): the pair layout when `conv_plan` asks for it, else
-        channels-last [F*B, N, cin_packed] bf16.  Returns (tensor, rows)."""
+    def forward_points(self, x, fix_loc, fixation_size=None, conv_plan=None, out=None, row_order="fb"):
+        """All fixations sampled straight into the layout the first KNNConv consumes: the pair layout when `conv_plan`
+        asks for it, else channels-last [rows, N, cin_packed] bf16.  Rows are ordered '(f b)' as fovi/fovinet.py:281
+        flattens them (row_order "fb"), or '(b f)' (row_order "bf": the fixations of an image next to each other, which is
+        what a pipeline cutting the batch into chunks of images wants).  Returns (tensor, rows)."""
+        if row_order not in ("fb", "bf"):
+            raise ValueError("row_order must be 'fb' or 'bf'")
         B, _, H, W = x.shape
         fix_loc, fixation_size = self._defaults(fix_loc, fixation_size)
         fix_rc, _ = _as_bf2(fix_loc, B, x.device, "fix_loc")
@@ -172,11 +179,12 @@ class RetinalTransform(nn.Module):
         F = fix_rc.shape[1]
         if fix_hw.shape[1] != F:
             fix_hw = self._expanded(fix_hw, B, F)
+        fb = row_order == "fb"
         if conv_plan is not None and conv_plan.x_layout == ops.X_PAIRS:
-            y = self.sampler.sample(x, fix_rc, fix_hw, layout=ops.OUT_FB_PAIRS, out=out)
+            y = self.sampler.sample(x, fix_rc, fix_hw, layout=ops.OUT_FB_PAIRS if fb else ops.OUT_BF_PAIRS, out=out)
         else:
             cp = 8 if conv_plan is None else conv_plan.cin_packed
-            y = self.sampler.sample(x, fix_rc, fix_hw, out_dtype=torch.bfloat16, layout=ops.OUT_FBNC, channel_stride=cp, out=out)
+            y = self.sampler.sample(x, fix_rc, fix_hw, out_dtype=torch.bfloat16, layout=ops.OUT_FBNC if fb else ops.OUT_BFNC, channel_stride=cp, out=out)
             y = y.reshape(F * B, y.shape[2], cp)
         return y, F * B
 

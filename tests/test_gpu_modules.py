@@ -174,3 +174,38 @@ def test_layer_on_natively_built_tables_matches_oracle(golden):
     ref = oracle.knnconv_forward(x.cpu().numpy(), layer.knn_indices_pad_token.numpy(), layer.tap.numpy(), V,
                                  layer.weight.detach().cpu().numpy(), layer.bias.detach().cpu().numpy())
     assert rel_l2(y, ref) < 1e-2
+
+
+def test_front_end_host_pipeline_equals_device_path(golden):
+    """run_from_host (pinned host buffers, chunked three-stream pipeline, rows '(b f)') gives the device path's numbers,
+    for float32 and bf16 host images; its copy-only mode touches nothing but the copies."""
+    from fovi_b200.coords import get_in_out_coords
+    from fovi_b200.knn import KNNConvLayer, KNNConvStack
+    from fovi_b200.pipeline import FoveatedFrontEnd
+    from fovi_b200.sensing import RetinalTransform
+    rt = RetinalTransform(resolution=20, start_res=64, fov=16, cmf_a=1.0, sampler="grid_bilinear", fixation_size=64, device="cuda",
+                          auto_match_cart_resources=0)
+    ic = rt.sampler.coords
+    _, oc, _ = get_in_out_coords(20, 16, 1.0, 2, auto_match_cart_resources=0)
+    torch.manual_seed(3)
+    l0 = KNNConvLayer(3, 64, 9, ic, oc, device="cuda", ref_frame_side_length=3, bias=True)
+    l1 = KNNConvLayer(64, 32, 9, oc, oc, device="cuda", ref_frame_side_length=3, bias=True)
+    front = FoveatedFrontEnd(rt, KNNConvStack([l0, l1]))
+    B, F = 11, 3
+    img = torch.from_numpy(synth_images(9, (B, 3, 64, 64))).pin_memory()
+    fix = torch.from_numpy((0.2 + 0.6 * np.random.RandomState(2).random_sample((B, F, 2))).astype(f32)).pin_memory()
+    out = torch.zeros((B, F, len(oc), 32), dtype=torch.bfloat16).pin_memory()
+    for x in (img, img.to(torch.bfloat16).pin_memory()):
+        out.zero_()
+        front.run_from_host(x, fix, out, chunks=4)
+        torch.cuda.synchronize()
+        want = front.forward(x.cuda(), fix.cuda()).view(F, B, len(oc), 32).permute(1, 0, 2, 3)
+        assert torch.equal(out, want.cpu())
+        keep = out.clone()
+        front.run_from_host(x, fix, out, chunks=4, kernels=False)        # copies only: the slot buffers still hold the last chunks
+        torch.cuda.synchronize()
+        assert out.shape == keep.shape
+    # the device path returns new memory on every call
+    a = front.forward(img.cuda(), fix.cuda()); b = front.forward(img.cuda(), fix.cuda())
+    assert a.data_ptr() != b.data_ptr() and torch.equal(a, b)
+    rt.sampler.check()
