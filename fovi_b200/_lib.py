@@ -48,6 +48,10 @@ SIGNATURES = {
     "fovi_tap_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_knnpool_plan_create": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
     "fovi_knnpool_plan_destroy": (None, [_P]),
+    "fovi_knnpool_set_weights": (C.c_int, [_P, _P]),
+    "fovi_knn_norm_stat_groups": (C.c_int64, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "fovi_knn_norm_forward": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, C.c_float, C.c_int, _P, _P,
+                                        C.c_int, _P]),
     "fovi_knnpool_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "fovi_launch_count": (C.c_int64, []),
 }

@@ -4,7 +4,8 @@
 
 Inference only.  A block is conv -> norm -> activation -> pool; here batch normalisation (the norm of every shipped
 configuration, fovi/arch/norm.py:36-48, evaluated with its running statistics) is folded into the convolution's packed
-weights and bias, ReLU runs in the convolution's epilogue, and pooling is the gather-reduce kernel on the same
+weights and bias and ReLU runs in the convolution's epilogue; a per-sample norm (channel / coord / layer / group) runs
+as its own kernel behind the convolution with the ReLU fused into it; pooling is the gather-reduce kernel on the same
 channels-last layout, so activations stay in the kernels' layout from the sensor to the classifier.
 """
 import numpy as np
@@ -14,38 +15,9 @@ import torch.nn as nn
 from . import ops
 from .coords import auto_match_num_coords, get_in_out_coords
 from .knn import KNNConvLayer, KNNPoolingLayer, get_knn_conv_layer
+from .norm import KNNBatchNorm, _KernelNorm, get_norm
 
-__all__ = ["KNNBatchNorm", "get_norm", "KNNAlexNetBlock", "KNNAlexNet", "FoveatedAlexNet"]
-
-
-class KNNBatchNorm(nn.BatchNorm1d):
-    """Batch normalisation over [B, C, N] activations (fovi/arch/norm.py:36-48)."""
-
-    def __init__(self, num_coords, num_channels, device="cuda"):
-        super().__init__(num_channels, device=device)
-
-    def __repr__(self):
-        return super().__repr__().replace("BatchNorm1d", "KNNBatchNorm")
-
-    def folded(self):
-        """Per-channel (scale, shift) of the evaluation-mode transform y = x*scale + shift, float32."""
-        scale = torch.rsqrt(self.running_var.float() + self.eps)
-        if self.weight is not None:
-            scale = scale * self.weight.detach().float()
-        shift = -self.running_mean.float() * scale
-        if self.bias is not None:
-            shift = shift + self.bias.detach().float()
-        return scale, shift
-
-
-def get_norm(norm_type, num_coords, num_channels, device="cuda"):
-    """Normalisation layer by name (fovi/arch/norm.py:126-160).  Built: every name containing 'batch', and 'none'.
-    The per-sample norms (channel / coord / layer / group) are not built."""
-    if "batch" in norm_type:
-        return KNNBatchNorm(num_coords, num_channels, device=device)
-    if norm_type == "none":
-        return None
-    raise NotImplementedError(f"norm_type {norm_type!r}: 'batch' and 'none' are built")
+__all__ = ["KNNBatchNorm", "get_norm", "KNNAlexNetBlock", "KNNAlexNet", "FoveatedAlexNet"]   # the norms live in fovi_b200/norm.py
 
 
 class KNNAlexNetBlock(nn.Module):
@@ -81,7 +53,7 @@ class KNNAlexNetBlock(nn.Module):
     # ---- the convolution's operands with the evaluation-mode batch norm folded in
     def _fold_key(self):
         ts = [self.conv.weight, self.conv.bias]
-        if self.norm is not None:
+        if isinstance(self.norm, KNNBatchNorm):
             ts += [self.norm.weight, self.norm.bias, self.norm.running_mean, self.norm.running_var]
         return tuple((t._version, t.data_ptr()) for t in ts if t is not None)
 
@@ -99,7 +71,7 @@ class KNNAlexNetBlock(nn.Module):
         if self._folded is None or self._folded[0] != key:
             w = self.conv.weight.detach().float()
             b = self.conv.bias.detach().float() if self.conv.bias is not None else None
-            if self.norm is not None:
+            if isinstance(self.norm, KNNBatchNorm):
                 scale, shift = self.norm.folded()
                 w = w * scale[:, None]
                 b = shift if b is None else b * scale + shift
@@ -110,16 +82,19 @@ class KNNAlexNetBlock(nn.Module):
     def points_path(self):
         """True when the block can run on the kernels' channels-last layout end to end."""
         return (self.conv is not None and self.conv.plan.tc_supported and getattr(self.conv, "precision", "bf16") == "bf16"
-                and (self.norm is None or isinstance(self.norm, KNNBatchNorm)))
+                and (self.norm is None or isinstance(self.norm, (KNNBatchNorm, _KernelNorm))))
 
     @torch.no_grad()
     def forward_points(self, h, rows):
         """h: the convolution's input layout (KNNConvLayer.forward_points) -> channels-last [rows, N_out, C_out] bf16."""
-        if self.norm is not None and self.norm.training:
+        if isinstance(self.norm, KNNBatchNorm) and self.norm.training:
             raise RuntimeError("KNNAlexNetBlock runs batch norm from its running statistics: call .eval() first")
         wt, b = self.folded_operands()
         relu = isinstance(self.activation, nn.ReLU)
-        h = self.conv.plan.forward(h, wt, b, relu=relu, out_dtype=torch.bfloat16, batch=rows)
+        per_sample = isinstance(self.norm, _KernelNorm)
+        h = self.conv.plan.forward(h, wt, b, relu=relu and not per_sample, out_dtype=torch.bfloat16, batch=rows)
+        if per_sample:
+            h = self.norm.forward_points(h, relu=relu)
         if self.activation is not None and not relu:
             h = self.activation(h)
         if self.pool is not None:
@@ -135,7 +110,7 @@ class KNNAlexNetBlock(nn.Module):
         if self.conv is not None:
             x = self.conv(x)
         if self.norm is not None:
-            if self.norm.training:
+            if isinstance(self.norm, KNNBatchNorm) and self.norm.training:
                 raise RuntimeError("KNNAlexNetBlock runs batch norm from its running statistics: call .eval() first")
             x = self.norm(x)
         if self.activation is not None:

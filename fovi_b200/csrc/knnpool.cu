@@ -14,30 +14,37 @@
 struct fovi_knnpool_plan {
   int n_in = 0, n_out = 0, K = 0;
   int* idx = nullptr;   // [n_out, K] neighbour indices, pad = n_in
+  float* wgt = nullptr; // [n_out, K] neighbour weights of the 'gaussian' mode (null until set)
 };
 
 namespace {
 
+// MODE 0 max, 1 mean, 2 sum, 3 weighted mean: sum_k x_k * w_k / (sum of the weights of the valid neighbours + 1e-8), the
+// 'gaussian' pooling of the reference (fovi/arch/knn.py:372-394: weights of pad / NaN neighbours are dropped and the rest
+// renormalised).
 template <typename T, int MODE>
-__global__ void knnpool_kernel(const T* __restrict__ X, T* __restrict__ Y, const int* __restrict__ idx, int B, int C, int n_in,
-                               int n_out, int K, int bnc) {
+__global__ void knnpool_kernel(const T* __restrict__ X, T* __restrict__ Y, const int* __restrict__ idx, const float* __restrict__ wgt, int B,
+                               int C, int n_in, int n_out, int K, int bnc) {
   const long long total = (long long)B * C * n_out;
   for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
     int b, c, n;
     if (bnc) { c = (int)(e % C); n = (int)((e / C) % n_out); b = (int)(e / ((long long)C * n_out)); }
     else { n = (int)(e % n_out); c = (int)((e / n_out) % C); b = (int)(e / ((long long)C * n_out)); }
     const int* nb = idx + (long long)n * K;
-    float acc = MODE == 0 ? -INFINITY : 0.f;
+    float acc = MODE == 0 ? -INFINITY : 0.f, wsum = 0.f;
     int cnt = 0;
     for (int k = 0; k < K; ++k) {
       const int j = __ldg(nb + k);
       if (j >= n_in) continue;
       const float v = ld_as_float(bnc ? X + ((long long)b * n_in + j) * C + c : X + ((long long)b * C + c) * n_in + j);
       if (v != v) continue;   // NaN: ignored
-      if (MODE == 0) acc = fmaxf(acc, v); else acc += v;
+      if (MODE == 0) acc = fmaxf(acc, v);
+      else if (MODE == 3) { const float w = __ldg(wgt + (long long)n * K + k); acc = fmaf(v, w, acc); wsum += w; }
+      else acc += v;
       ++cnt;
     }
     if (MODE == 1) acc = acc / (float)cnt;   // no valid neighbour: 0/0 = NaN, as nanmean
+    if (MODE == 3) acc = acc / (wsum + 1e-8f);
     Y[e] = from_float<T>(acc);
   }
 }
@@ -106,12 +113,24 @@ extern "C" int fovi_knnpool_plan_create(const int32_t* knn_idx_pad, int n_in, in
 extern "C" void fovi_knnpool_plan_destroy(fovi_knnpool_plan* p) {
   if (!p) return;
   if (p->idx) cudaFree(p->idx);
+  if (p->wgt) cudaFree(p->wgt);
   delete p;
+}
+
+extern "C" int fovi_knnpool_set_weights(fovi_knnpool_plan* p, const float* w_kn) {
+  if (!p || !w_kn) return FOVI_ERR_INVALID_ARGUMENT;
+  std::vector<float> t((size_t)p->n_out * p->K);
+  for (int k = 0; k < p->K; ++k)
+    for (int n = 0; n < p->n_out; ++n) t[(size_t)n * p->K + k] = w_kn[(size_t)k * p->n_out + n];
+  if (!p->wgt) FOVI_CUDA(cudaMalloc(&p->wgt, sizeof(float) * t.size()));
+  FOVI_CUDA(cudaMemcpy(p->wgt, t.data(), sizeof(float) * t.size(), cudaMemcpyHostToDevice));
+  return FOVI_OK;
 }
 
 extern "C" int fovi_knnpool_forward(const fovi_knnpool_plan* p, const void* X, int dtype, int layout, int B, int C, int mode,
                                     void* Y, void* stream) {
-  if (!p || !fovi::valid_dtype(dtype) || B < 0 || C <= 0 || mode < 0 || mode > 2) return FOVI_ERR_INVALID_ARGUMENT;
+  if (!p || !fovi::valid_dtype(dtype) || B < 0 || C <= 0 || mode < 0 || mode > 3) return FOVI_ERR_INVALID_ARGUMENT;
+  if (mode == 3 && !p->wgt) return FOVI_ERR_INVALID_ARGUMENT;   // fovi_knnpool_set_weights first
   if (layout != FOVI_ACT_BCN && layout != FOVI_ACT_BNC) return FOVI_ERR_INVALID_ARGUMENT;
   if (B == 0) return FOVI_OK;
   if (!X || !Y) return FOVI_ERR_INVALID_ARGUMENT;
@@ -119,7 +138,7 @@ extern "C" int fovi_knnpool_forward(const fovi_knnpool_plan* p, const void* X, i
   const long long total = (long long)B * C * p->n_out;
   const int grid = (int)std::min<long long>((total + 255) / 256, (long long)fovi::sm_count() * 32);
   const int bnc = layout == FOVI_ACT_BNC;
-  if (bnc && dtype == FOVI_BF16 && C % 8 == 0 && (reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) % 16 == 0) {
+  if (mode != 3 && bnc && dtype == FOVI_BF16 && C % 8 == 0 && (reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(Y)) % 16 == 0) {
     const long long tot8 = total / 8;
     const int g8 = (int)std::min<long long>((tot8 + 255) / 256, (long long)fovi::sm_count() * 32);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
@@ -129,9 +148,9 @@ extern "C" int fovi_knnpool_forward(const fovi_knnpool_plan* p, const void* X, i
     else knnpool_bnc8_kernel<2><<<g8, 256, 0, st>>>(x, y, p->idx, B, C, p->n_in, p->n_out, p->K);
     return fovi::after_launch("knnpool_bnc8_kernel");
   }
-#define RUN(T, M) knnpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)X, (T*)Y, p->idx, B, C, p->n_in, p->n_out, p->K, bnc)
-  if (dtype == FOVI_F32) { if (mode == 0) RUN(float, 0); else if (mode == 1) RUN(float, 1); else RUN(float, 2); }
-  else { if (mode == 0) RUN(__nv_bfloat16, 0); else if (mode == 1) RUN(__nv_bfloat16, 1); else RUN(__nv_bfloat16, 2); }
+#define RUN(T, M) knnpool_kernel<T, M><<<grid, 256, 0, st>>>((const T*)X, (T*)Y, p->idx, p->wgt, B, C, p->n_in, p->n_out, p->K, bnc)
+  if (dtype == FOVI_F32) { if (mode == 0) RUN(float, 0); else if (mode == 1) RUN(float, 1); else if (mode == 2) RUN(float, 2); else RUN(float, 3); }
+  else { if (mode == 0) RUN(__nv_bfloat16, 0); else if (mode == 1) RUN(__nv_bfloat16, 1); else if (mode == 2) RUN(__nv_bfloat16, 2); else RUN(__nv_bfloat16, 3); }
 #undef RUN
   return fovi::after_launch("knnpool_kernel");
 }

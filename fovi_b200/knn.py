@@ -20,14 +20,14 @@ __all__ = ["KNNPoolingLayer", "KNNConvLayer", "KNNDepthwiseConvLayer", "KNNDepth
 
 
 class KNNPoolingLayer(nn.Module):
-    """Pooling over the K nearest neighbours; counterpart of the reference layer (fovi/arch/knn.py:276-397) for
-    the modes 'max', 'avg' and 'sum' ('gaussian' is not built).  forward(X [B,C,N_in]) -> [B,C,N_out]."""
+    """Pooling over the K nearest neighbours; counterpart of the reference layer (fovi/arch/knn.py:276-397): modes 'max',
+    'avg', 'sum' and 'gaussian' (distance-weighted mean).  forward(X [B,C,N_in]) -> [B,C,N_out]."""
 
     def __init__(self, k, in_coords, out_coords, mode="max", device="cuda", sample_cortex=True, gauss_sigma=10, batch_size=None,
                  table_builder=None):
         super().__init__()
         if mode not in ops.POOL_MODES:
-            raise NotImplementedError(f"pooling mode {mode!r}: 'max', 'avg' and 'sum' are built")
+            raise NotImplementedError(f"Pooling style {mode} not implemented")
         self.in_coords, self.out_coords, self.device, self.mode = in_coords, out_coords, device, mode
         self.sample_cortex, self.batch_size = sample_cortex, batch_size
         n_in = in_coords.shape[0]
@@ -38,6 +38,19 @@ class KNNPoolingLayer(nn.Module):
         self.knn_indices_pad_mask = self.knn_indices >= n_in
         self.knn_indices_pad_token = tables.pad_token_table(self.knn_indices, n_in)
         self._plan = ops.KnnPoolPlan(self.knn_indices_pad_token.numpy().astype(np.int32), n_in, device=torch.device(device))
+        if mode == "gaussian":
+            self.gauss_sigma = gauss_sigma
+            self.gaussian_weights = self._compute_gaussian_weights()
+            self._plan.set_weights(self.gaussian_weights.numpy())
+
+    def _compute_gaussian_weights(self):
+        """[K, n_out] weights exp(-d^2 / (2 sigma^2)) of the neighbour distances, min-max normalised per neighbourhood, summing
+        to one per output point (fovi/arch/knn.py:325-343; same torch operations, so the same numbers)."""
+        d = self.knn_distances
+        lo, hi = d.min(0).values.unsqueeze(0), d.max(0).values.unsqueeze(0)
+        k = (d - lo) / (hi - lo)
+        w = torch.exp(-k ** 2 / (2 * self.gauss_sigma ** 2))
+        return w / (w.sum(dim=0, keepdim=True) + 1e-8)
 
     @torch.no_grad()
     def forward(self, X_l):
@@ -249,8 +262,9 @@ class KNNDepthwiseConvLayer(_DepthwiseBase):
 class KNNDepthwiseSeparableConvLayer(_DepthwiseBase):
     """Depthwise KNN convolution followed by a pointwise linear map over channels (fovi/arch/knn.py:722-800).
     Parameters as the reference: ``dw_conv [C_in, V, g]``, ``p_conv`` = Linear(C_out, C_out); the base class's dense
-    ``weight`` is kept (unused, as in the reference) so that state dicts line up.  The pointwise map is a plain dense
-    matrix product on the channels-last depthwise output and is left to the library GEMM."""
+    ``weight`` is kept (unused, as in the reference) so that state dicts line up.  The pointwise map is a KNNConv whose
+    every point has itself as only neighbour (one tap), so it runs on the same kernels: the tensor-core kernel for bf16
+    activations, the exact float32 kernel otherwise."""
 
     def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True, bias=False,
                  batch_size=None, ref_frame_side_length=None, **kwargs):
@@ -265,12 +279,30 @@ class KNNDepthwiseSeparableConvLayer(_DepthwiseBase):
         nn.init.uniform_(self.p_conv.weight, a=-bound, b=bound)
         if self.p_conv.bias is not None:
             nn.init.zeros_(self.p_conv.bias)
+        n_out = self.knn_indices.shape[1]
+        self._pw_plan = ops.KnnConvPlan(np.arange(n_out, dtype=np.int32)[None, :], np.zeros((n_out, 1), np.uint16), n_out, 1,
+                                        out_channels, out_channels, device=dev)
+
+    def _packed_pointwise(self, dtype):
+        w = self.p_conv.weight
+        key, name = (w._version, w.data_ptr()), ("pw", dtype)
+        hit = self._packed.get(name)
+        if hit is None or hit[0] != key:
+            self._packed[name] = (key, self._pw_plan.pack_weights(w.detach(), dtype))
+        return self._packed[name][1]
 
     def forward(self, X_l):
         self._check_no_grad(X_l, self.dw_conv, self.p_conv.weight)
         with torch.no_grad():
-            dw = self._plan.depthwise(X_l, self._packed_depthwise(self.dw_conv), None, y_layout=ops.ACT_BNC)     # [B, N_out, C_out]
-            return self.p_conv(dw).transpose(1, 2)
+            tc = X_l.dtype == torch.bfloat16 and self._pw_plan.tc_supported and self._pw_plan.x_layout == ops.X_BNC \
+                and self._pw_plan.cin_packed == self.out_channels
+            dw = self._plan.depthwise(X_l, self._packed_depthwise(self.dw_conv), None, y_layout=ops.ACT_BNC,
+                                      out_dtype=torch.bfloat16 if tc else torch.float32)                          # [B, N_out, C_out]
+            if tc:
+                y = self._pw_plan.forward(dw, self._packed_pointwise(torch.bfloat16), self.p_conv.bias, out_dtype=torch.bfloat16)
+                return y.permute(0, 2, 1)
+            y = self._pw_plan.forward_f32(dw, self._packed_pointwise(torch.float32), self.p_conv.bias, x_layout=ops.ACT_BNC)
+            return y.to(X_l.dtype)
 
 
 class KNNPatchEmbedding(KNNConvLayer):

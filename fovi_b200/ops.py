@@ -323,7 +323,8 @@ def sample_knnconv_fused(splan, cplan, img, fix_rc, fix_hw, wt, bias=None, relu=
     return out, intermediate
 
 
-POOL_MODES = {"max": 0, "avg": 1, "sum": 2}
+POOL_MODES = {"max": 0, "avg": 1, "sum": 2, "gaussian": 3}
+NORM_MODES = {"channel": 0, "coord": 1, "layer": 2, "group": 3}
 
 
 class KnnPoolPlan:
@@ -344,6 +345,13 @@ class KnnPoolPlan:
         if h and lib is not None:
             lib.fovi_knnpool_plan_destroy(h)
 
+    def set_weights(self, w_kn):
+        """Neighbour weights [K, n_out] float32 of the 'gaussian' mode (KNNPoolingLayer.gaussian_weights)."""
+        w = np.ascontiguousarray(np.asarray(w_kn, np.float32))
+        assert w.shape == (self.K, self.n_out), w.shape
+        with torch.cuda.device(self.device):
+            check(lib.fovi_knnpool_set_weights(self._h, w.ctypes.data_as(C.c_void_p)), "fovi_knnpool_set_weights")
+
     def forward(self, x, mode="max", layout=ACT_BCN):
         """x [B,C,n_in] (ACT_BCN) or [B,n_in,C] (ACT_BNC), float32 or bf16 -> same layout with n_out points."""
         _need_cuda(x)
@@ -355,6 +363,34 @@ class KnnPoolPlan:
         with torch.cuda.device(x.device):
             check(lib.fovi_knnpool_forward(self._h, _ptr(x), _dt(x.dtype), layout, B, Cc, POOL_MODES[mode], _ptr(y), _stream()), "fovi_knnpool_forward")
         return y
+
+
+def knn_norm(x, mode, weight=None, bias=None, eps=1e-5, groups=1, layout=ACT_BCN, relu=False, out_dtype=None):
+    """Per-sample normalisation of x ([B,C,N] for ACT_BCN, [B,N,C] for ACT_BNC; float32 or bf16) over the channels
+    ('channel'), the points ('coord'), both ('layer') or channel groups x points ('group'); weight / bias float32 of the
+    shape the mode asks for (see fovi_knn_norm_forward).  Returns the same layout in `out_dtype` (default: x's)."""
+    _need_cuda(x, weight, bias)
+    x = x.contiguous()
+    B = x.shape[0]
+    Cc, N = (x.shape[1], x.shape[2]) if layout == ACT_BCN else (x.shape[2], x.shape[1])
+    m = NORM_MODES[mode]
+    ng = lib.fovi_knn_norm_stat_groups(m, B, Cc, N, int(groups))
+    if ng < 0:
+        raise ValueError(f"{Cc} channels do not split into {groups} groups")
+    want = {"channel": Cc, "coord": N, "layer": Cc * N, "group": Cc}[mode]
+    prm = []
+    for t in (weight, bias):
+        if t is not None:
+            t = t.detach().to(torch.float32).contiguous()
+            assert t.numel() == want, (mode, tuple(t.shape), want)
+        prm.append(t)
+    stats = torch.empty((max(ng, 1), 2), dtype=torch.float32, device=x.device)
+    y = torch.empty_like(x, dtype=x.dtype if out_dtype is None else out_dtype)
+    with torch.cuda.device(x.device):
+        check(lib.fovi_knn_norm_forward(_ptr(x), _dt(x.dtype), layout, B, Cc, N, m, int(groups), _ptr(prm[0]) if prm[0] is not None else None,
+                                        _ptr(prm[1]) if prm[1] is not None else None, float(eps), int(relu), _ptr(stats), _ptr(y), _dt(y.dtype),
+                                        _stream()), "fovi_knn_norm_forward")
+    return y
 
 
 def pack_points(x, cp=8, x_layout=X_BNC):

@@ -282,15 +282,20 @@ int fovi_tap_table_build(const int32_t* knn_idx, int K, int n_out, const float* 
 
 /* ------------------------------------------------------------------------------------------
  * KNN pooling.
- * Replaces KNNPoolingLayer.forward (fovi/arch/knn.py:345-394) for the modes 'max', 'avg', 'sum':
- * reduction over the K neighbours of each output point, pad neighbours (and NaN inputs) ignored.
+ * Replaces KNNPoolingLayer.forward (fovi/arch/knn.py:345-394) for the modes 'max', 'avg', 'sum' and
+ * 'gaussian': reduction over the K neighbours of each output point, pad neighbours (and NaN inputs)
+ * ignored.
  * ------------------------------------------------------------------------------------------ */
 typedef struct fovi_knnpool_plan fovi_knnpool_plan;
-typedef enum { FOVI_POOL_MAX = 0, FOVI_POOL_AVG = 1, FOVI_POOL_SUM = 2 } fovi_pool_mode;
+typedef enum { FOVI_POOL_MAX = 0, FOVI_POOL_AVG = 1, FOVI_POOL_SUM = 2, FOVI_POOL_WEIGHTED = 3 } fovi_pool_mode;
 
 /* knn_idx_pad: HOST [K,n_out] int32 — KNNPoolingLayer.knn_indices_pad_token (knn.py:316-319). */
 int fovi_knnpool_plan_create(const int32_t* knn_idx_pad, int n_in, int n_out, int K, fovi_knnpool_plan** out);
 void fovi_knnpool_plan_destroy(fovi_knnpool_plan* plan);
+/* Neighbour weights of FOVI_POOL_WEIGHTED: w_kn HOST [K,n_out] float32 — KNNPoolingLayer.gaussian_weights
+ * (knn.py:325-343).  The forward drops the weights of pad / NaN neighbours and renormalises the rest:
+ * y = sum_k x_k w_k / (sum of valid w_k + 1e-8), knn.py:372-390.  Synchronises the device. */
+int fovi_knnpool_set_weights(fovi_knnpool_plan* plan, const float* w_kn);
 /* X: [B,C,n_in] (FOVI_ACT_BCN) or [B,n_in,C] (FOVI_ACT_BNC) of `dtype`; Y: same layout and dtype with n_out
  * points.  An output point without any valid neighbour gives -inf (max), NaN (avg), 0 (sum), as the reference. */
 int fovi_knnpool_forward(const fovi_knnpool_plan* plan, const void* X, int dtype, int layout, int B, int C, int mode,
@@ -298,6 +303,24 @@ int fovi_knnpool_forward(const fovi_knnpool_plan* plan, const void* X, int dtype
 
 /* Number of kernels this library has launched from the calling process (all entry points). */
 int64_t fovi_launch_count(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Per-sample normalisation of KNN activations.
+ * Replaces KNNChannelNorm / KNNCoordNorm / KNNLayerNorm / KNNGroupNorm .forward
+ * (fovi/arch/norm.py:14-101: torch LayerNorm over [C], [N] or [C,N], GroupNorm over channel groups,
+ * applied to [B,C,N]):  y = (x - mean) / sqrt(var + eps) * weight + bias  with the biased variance of
+ *   FOVI_NORM_CHANNEL : the C channels of every (sample, point);        weight, bias [C]
+ *   FOVI_NORM_COORD   : the N points of every (sample, channel);        weight, bias [N]
+ *   FOVI_NORM_LAYER   : all C*N values of a sample;                     weight, bias [C,N]
+ *   FOVI_NORM_GROUP   : N points x C/groups channels of every group;    weight, bias [C]
+ * x, y: [B,C,N] (FOVI_ACT_BCN) or [B,N,C] (FOVI_ACT_BNC), same layout; weight / bias: DEVICE float32
+ * or NULL; stats: DEVICE scratch of 2 * fovi_knn_norm_stat_groups(...) float32 (receives mean and
+ * 1/std of every statistics group); relu: apply max(.,0) last.
+ * ------------------------------------------------------------------------------------------ */
+typedef enum { FOVI_NORM_CHANNEL = 0, FOVI_NORM_COORD = 1, FOVI_NORM_LAYER = 2, FOVI_NORM_GROUP = 3 } fovi_norm_mode;
+int64_t fovi_knn_norm_stat_groups(int mode, int B, int C, int N, int groups);
+int fovi_knn_norm_forward(const void* x, int x_dtype, int layout, int B, int C, int N, int mode, int groups, const float* weight,
+                          const float* bias, float eps, int relu, float* stats, void* y, int y_dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -320,3 +320,43 @@ def knn_pool_avg(X, knn_idx_pad):
     cnt = (~np.isnan(g)).sum(2).astype(f32)
     with np.errstate(invalid="ignore", divide="ignore"):
         return (knn_pool_sum(X, knn_idx_pad) / cnt).astype(f32)
+
+
+def knn_pool_weighted(X, knn_idx_pad, weights):
+    """'gaussian' pooling (fovi/arch/knn.py:372-390): weighted mean over the valid neighbours with the weights of pad / NaN
+    neighbours dropped and the rest renormalised, ``sum_k x_k w_k / (sum_valid w_k + 1e-8)``.  weights [K, n_out]."""
+    g = _pool_gather(np.asarray(X, np.float64), knn_idx_pad)          # [B,C,K,n_out], NaN at pad neighbours
+    valid = ~np.isnan(g)
+    w = np.where(valid, np.asarray(weights, np.float64)[None, None], 0.0)
+    w = w / (w.sum(2, keepdims=True) + 1e-8)
+    return (np.where(valid, g, 0.0) * w).sum(2).astype(f32)
+
+
+def knn_norm(X, mode, weight=None, bias=None, eps=1e-5, groups=1):
+    """Per-sample norms of [B,C,N] activations (fovi/arch/norm.py:14-101 = torch LayerNorm / GroupNorm, biased variance):
+    'channel' over C, 'coord' over N, 'layer' over (C, N), 'group' over (C/groups, N).  weight / bias broadcast as torch
+    does: [C] for channel and group, [N] for coord, [C, N] for layer."""
+    X = np.asarray(X, np.float64)
+    B, C, N = X.shape
+    if mode == "channel":
+        m, v = X.mean(1, keepdims=True), X.var(1, keepdims=True)
+        shape = (1, C, 1)
+    elif mode == "coord":
+        m, v = X.mean(2, keepdims=True), X.var(2, keepdims=True)
+        shape = (1, 1, N)
+    elif mode == "layer":
+        m, v = X.mean((1, 2), keepdims=True), X.var((1, 2), keepdims=True)
+        shape = (1, C, N)
+    elif mode == "group":
+        Xg = X.reshape(B, groups, (C // groups) * N)
+        m = np.repeat(Xg.mean(2), C // groups, 1)[:, :, None]
+        v = np.repeat(Xg.var(2), C // groups, 1)[:, :, None]
+        shape = (1, C, 1)
+    else:
+        raise ValueError(mode)
+    y = (X - m) / np.sqrt(v + eps)
+    if weight is not None:
+        y = y * np.asarray(weight, np.float64).reshape(shape)
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64).reshape(shape)
+    return y.astype(f32)

@@ -213,10 +213,46 @@ def depthwise_fixture(save, knn):
     print("depthwise fixture: n_in", len(ic), "n_out", len(oc), "V", V, "state keys", sorted(sep.state_dict().keys()), sorted(dw.state_dict().keys()))
 
 
+def norms_fixture(save, knn):
+    """The per-sample norm layers (fovi/arch/norm.py) and 'gaussian' pooling (fovi/arch/knn.py:321-394), run on CPU."""
+    import fovi.arch.norm as norm
+    rs = np.random.RandomState(51)
+    B, C, N = 3, 24, 37
+    x = (rs.standard_normal((B, C, N)) * 1.5 + 0.3).astype(f32)
+    out = {"seed": np.int64(51), "x_shape": np.array([B, C, N])}
+    for name, cls, wshape, mode, kw in (("channel", norm.KNNChannelNorm, (C,), "channel", {}), ("coord", norm.KNNCoordNorm, (N,), "coord", {}),
+                                        ("layer", norm.KNNLayerNorm, (C, N), "layer", {}), ("group", norm.KNNGroupNorm, (C,), "group", {})):
+        layer = cls(N, C, device="cpu", **kw)
+        w = (0.5 + rs.random_sample(wshape)).astype(f32)
+        b = (0.2 * rs.standard_normal(wshape)).astype(f32)
+        layer.weight.data.copy_(torch.from_numpy(w)); layer.bias.data.copy_(torch.from_numpy(b))
+        y = layer(torch.from_numpy(x)).numpy()
+        groups = layer.num_groups if name == "group" else 1
+        o = oracle.knn_norm(x, mode, w, b, eps=layer.eps, groups=groups)
+        assert np.abs(o - y).max() < 2e-6, (name, np.abs(o - y).max())
+        out[f"{name}_w"], out[f"{name}_b"], out[f"{name}_out"], out[f"{name}_groups"] = w, b, y, np.int64(groups)
+        assert sorted(layer.state_dict().keys()) == ["bias", "weight"]
+    assert norm.find_valid_num_groups(24, 32) == 6 and norm.find_valid_num_groups(96, 32) == 24 and norm.find_valid_num_groups(7, 32) == 1
+    # gaussian pooling on a small sensor pair
+    ic, oc, _ = knn.get_in_out_coords(24, 16, 1.0, 2, style="isotropic", auto_match_cart_resources=0, device="cpu")
+    pool = knn.KNNPoolingLayer(9, ic, oc, mode="gaussian", device="cpu", gauss_sigma=0.6)
+    xp = (rs.standard_normal((2, 5, len(ic)))).astype(f32)
+    xp[0, 1, 7] = np.nan                                            # a NaN input is dropped like a pad neighbour
+    yp = pool(torch.from_numpy(xp)).numpy()
+    idxp = pool.knn_indices_pad_token.numpy().astype(np.int32)
+    gw = pool.gaussian_weights.numpy()
+    o = oracle.knn_pool_weighted(xp, idxp, gw)
+    assert np.allclose(o, yp, rtol=1e-5, atol=1e-6, equal_nan=True), np.nanmax(np.abs(o - yp))
+    out.update(pool_x=xp, pool_out=yp, pool_knn_idx_pad=idxp, pool_knn_idx=pool.knn_indices.numpy().astype(np.int32),
+               pool_weights=gw, pool_distances=pool.knn_distances.numpy(), pool_n_in=np.int64(len(ic)), pool_sigma=np.float64(0.6))
+    save("norms_small.npz", **out)
+    print("norms fixture: groups", int(out["group_groups"]), "pool n_in", len(ic), "n_out", len(oc))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
-    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise"], help="regenerate one fixture group only")
+    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise", "norms"], help="regenerate one fixture group only")
     args = ap.parse_args()
     knn, retina, coords, knnvit = load_reference(args.reference)
     torch.set_grad_enabled(False)
@@ -227,6 +263,8 @@ def main():
         return backward_fixture(save, knn)
     if args.only == "depthwise":
         return depthwise_fixture(save, knn)
+    if args.only == "norms":
+        return norms_fixture(save, knn)
 
     # ------------------------------------------------------------ sensors (geometry fixtures)
     sensors = {}
@@ -395,6 +433,7 @@ def main():
     alexnet_fixture(save)
     backward_fixture(save, knn)
     depthwise_fixture(save, knn)
+    norms_fixture(save, knn)
 
 
 if __name__ == "__main__":

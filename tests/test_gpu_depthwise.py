@@ -77,3 +77,10 @@ def test_depthwise_separable_matches_reference_steps(golden):
         y = layer(torch.from_numpy(x).cuda())
     assert y.shape == g["dwsep_out"].shape
     assert rel_max(y.cpu().numpy(), g["dwsep_out"]) < 1e-3          # the pointwise product may run in TF32
+    # bf16 activations: the pointwise map runs on the tensor-core kernel (a KNNConv whose points are their own only neighbour)
+    with torch.no_grad():
+        yb = layer(torch.from_numpy(x).cuda().to(torch.bfloat16))
+    assert yb.dtype == torch.bfloat16 and yb.shape == g["dwsep_out"].shape
+    err = np.linalg.norm(yb.float().cpu().numpy() - g["dwsep_out"]) / np.linalg.norm(g["dwsep_out"])
+    assert err < 1e-2, err
+    layer._pw_plan.check()

@@ -158,3 +158,14 @@ def test_oracle_depthwise_matches_reference_steps(golden):
     b = (0.1 * rs.standard_normal(32)).astype(np.float32)
     o = oracle.knn_depthwise_forward(x, g["knn_idx_pad"], g["tap"].astype(np.int64), w, b)
     assert np.abs(o - g["dw_out"]).max() <= 1e-5 * np.abs(g["dw_out"]).max()
+
+
+def test_norms_and_gaussian_pooling_oracle(golden):
+    g = golden("norms_small.npz")
+    B, C, N = (int(v) for v in g["x_shape"])
+    x = (np.random.RandomState(int(g["seed"])).standard_normal((B, C, N)) * 1.5 + 0.3).astype(np.float32)
+    for name in ("channel", "coord", "layer", "group"):
+        o = oracle.knn_norm(x, name, g[f"{name}_w"], g[f"{name}_b"], groups=int(g[f"{name}_groups"]))
+        assert np.abs(o - g[f"{name}_out"]).max() < 2e-6, name
+    o = oracle.knn_pool_weighted(g["pool_x"], g["pool_knn_idx_pad"], g["pool_weights"])
+    assert np.allclose(o, g["pool_out"], rtol=1e-5, atol=1e-6, equal_nan=True)
