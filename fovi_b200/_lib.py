@@ -22,6 +22,7 @@ SIGNATURES = {
     "fovi_sample_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), _P, _P,
                                       C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_sampler_check": (C.c_int, [_P, _P]),
+    "fovi_sample_backward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P]),
     "fovi_knnconv_plan_create": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(_P)]),
     "fovi_knnconv_plan_destroy": (None, [_P]),
     "fovi_knnconv_cin_packed": (C.c_int, [_P]),
@@ -42,6 +43,7 @@ SIGNATURES = {
                                             C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_pack_weights_grouped": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_knn_depthwise_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_knn_depthwise_backward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),
     "fovi_column_sum": (C.c_int, [_P, C.c_int, C.c_longlong, C.c_int, _P, _P]),
     "fovi_batch_to_inner": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, _P, C.c_int, C.c_int, _P]),
     "fovi_knn_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P]),

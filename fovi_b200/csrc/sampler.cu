@@ -59,6 +59,7 @@ struct fovi_sampler_plan {
   int device = -1;
   float2* sorted_xy = nullptr;  // [N] grid (x, y) in Morton order (general kernel)
   int* sorted_idx = nullptr;    // [N] original index of each visited point
+  float2* grid_xy = nullptr;    // [N] grid (x, y) in the caller's order (gradient kernel)
   void* ys = nullptr;           // [N] {x, y, original index, 0} sorted by grid y (strip kernel); null: no such order
   float gx_min = 0, gx_max = 0, gy_min = 0, gy_max = 0;
   int* rank_lut = nullptr;      // [4097] rank table over gy buckets (see the strip kernel)
@@ -582,6 +583,55 @@ __global__ void __launch_bounds__(256, 3) fovi_sample_kernel(const SampleArgs a)
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Gradient with respect to the image (what autograd through F.grid_sample gives the reference, samplers.py:108): every
+// output gradient is scattered onto the taps of its footprint with the forward's weights.  One thread per
+// (image, fixation, point); float32 atomics into a zero-initialised (or accumulating) gradient image.
+// ------------------------------------------------------------------------------------------------------------
+template <typename TG, int MODE, int PAD>
+__global__ void __launch_bounds__(256) fovi_sample_backward_kernel(const SampleArgs a, const TG* __restrict__ gout, float* __restrict__ gimg) {
+  const long long total = (long long)a.B * a.F * a.N;
+  const float Wf = (float)a.W, Hf = (float)a.H;
+  const float sxw = Wf * 0.5f, syh = Hf * 0.5f, inv_w = 1.f / Wf, inv_h = 1.f / Hf;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int n = (int)(e % a.N);
+    const int bf = (int)(e / a.N);
+    const int b = bf / a.F, f = bf - b * a.F;
+    const float fr = __ldg(a.fix_rc + 2 * bf), fc = __ldg(a.fix_rc + 2 * bf + 1);
+    const float fh = __ldg(a.fix_hw + 2 * bf), fw = __ldg(a.fix_hw + 2 * bf + 1);
+    const float2 g = __ldg(a.sorted_xy + n);      // here: the grid in its ORIGINAL order
+    float ix = grid_to_pixel(g.x, __fdiv_rn(fw, 2.f), __fmul_rn(fc, Wf), Wf, inv_w, sxw, a.pow2);
+    float iy = grid_to_pixel(g.y, __fdiv_rn(fh, 2.f), __fmul_rn(fr, Hf), Hf, inv_h, syh, a.pow2);
+    if (PAD == FOVI_PAD_BORDER) {
+      ix = fminf(fmaxf(ix, 0.f), Wf - 1.f);
+      iy = fminf(fmaxf(iy, 0.f), Hf - 1.f);
+    }
+    const long long row = a.f_major ? ((long long)f * a.B + b) : (long long)bf;
+    const TG* go = gout + row * (long long)a.C * a.N + n;
+    float* gi = gimg + (long long)b * a.C * a.H * a.W;
+    if (MODE == FOVI_NEAREST) {
+      const int x = (int)rintf(ix), y = (int)rintf(iy);
+      if (x < 0 || x >= a.W || y < 0 || y >= a.H) continue;
+      for (int c = 0; c < a.C; ++c) atomicAdd(gi + ((long long)c * a.H + y) * a.W + x, ld_as_float(go + (long long)c * a.N));
+    } else {
+      const float x0f = floorf(ix), y0f = floorf(iy);
+      const float tx = __fsub_rn(ix, x0f), ty = __fsub_rn(iy, y0f);
+      const float ux = __fsub_rn(1.f, tx), uy = __fsub_rn(1.f, ty);
+      const float w4[4] = {__fmul_rn(uy, ux), __fmul_rn(uy, tx), __fmul_rn(ty, ux), __fmul_rn(ty, tx)};
+      const int x0 = (int)x0f, y0 = (int)y0f;
+      for (int c = 0; c < a.C; ++c) {
+        const float gv = ld_as_float(go + (long long)c * a.N);
+        float* plane = gi + (long long)c * a.H * a.W;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const int x = x0 + (t & 1), y = y0 + (t >> 1);
+          if (x >= 0 && x < a.W && y >= 0 && y < a.H) atomicAdd(plane + (long long)y * a.W + x, gv * w4[t]);
+        }
+      }
+    }
+  }
+}
+
 // Does the strip kernel apply?  Fills R, n_strips, pitch.
 template <typename TIn>
 bool plan_strips(SampleArgs& a, bool nc) {
@@ -697,6 +747,8 @@ extern "C" int fovi_sampler_plan_create(const float* grid_xy, int n_points, fovi
   if (e == cudaSuccess) e = cudaMalloc(&p->sorted_idx, sizeof(int) * n_points);
   if (e == cudaSuccess) e = cudaMemcpy(p->sorted_xy, xy.data(), sizeof(float2) * n_points, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(p->sorted_idx, idx.data(), sizeof(int) * n_points, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMalloc(&p->grid_xy, sizeof(float2) * n_points);
+  if (e == cudaSuccess) e = cudaMemcpy(p->grid_xy, grid_xy, sizeof(float2) * n_points, cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMalloc(&p->status, sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(p->status, 0, sizeof(int));
   if (e == cudaSuccess && finite) {
@@ -730,6 +782,7 @@ extern "C" void fovi_sampler_plan_destroy(fovi_sampler_plan* plan) {
   if (plan->sorted_xy) cudaFree(plan->sorted_xy);
   if (plan->sorted_idx) cudaFree(plan->sorted_idx);
   if (plan->ys) cudaFree(plan->ys);
+  if (plan->grid_xy) cudaFree(plan->grid_xy);
   if (plan->rank_lut) cudaFree(plan->rank_lut);
   if (plan->status) cudaFree(plan->status);
   delete plan;
@@ -790,4 +843,33 @@ extern "C" int fovi_sampler_check(fovi_sampler_plan* plan, void* stream) {
     return FOVI_ERR_DEVICE_TIMEOUT;
   }
   return FOVI_OK;
+}
+
+extern "C" int fovi_sample_backward(const fovi_sampler_plan* plan, const void* grad_out, int go_dtype, int layout, int B, int C, int H, int W,
+                                    const float* fix_rc, const float* fix_hw, int F, int mode, int pad, float* grad_img, void* stream) {
+  if (!plan || B < 0 || C <= 0 || H <= 0 || W <= 0 || F <= 0 || !fovi::valid_dtype(go_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
+  if (mode != FOVI_NEAREST && mode != FOVI_BILINEAR) return FOVI_ERR_INVALID_ARGUMENT;
+  if (pad != FOVI_PAD_ZEROS && pad != FOVI_PAD_BORDER) return FOVI_ERR_INVALID_ARGUMENT;
+  if (layout != FOVI_OUT_BFCN && layout != FOVI_OUT_FBCN) return FOVI_ERR_UNSUPPORTED;
+  if (B == 0) return FOVI_OK;
+  if (!grad_out || !fix_rc || !fix_hw || !grad_img || !plan->grid_xy) return FOVI_ERR_INVALID_ARGUMENT;
+  SampleArgs a;
+  memset(&a, 0, sizeof(a));
+  a.sorted_xy = plan->grid_xy; a.fix_rc = fix_rc; a.fix_hw = fix_hw;
+  a.B = B; a.C = C; a.H = H; a.W = W; a.F = F; a.N = plan->n_points;
+  a.f_major = layout == FOVI_OUT_FBCN ? 1 : 0;
+  a.pow2 = ((W & (W - 1)) == 0 && (H & (H - 1)) == 0) ? 1 : 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long total = (long long)B * F * plan->n_points;
+  const int grid = (int)std::min<long long>((total + 255) / 256, (long long)fovi::sm_count() * 32);
+#define RUN(TG, M, P) fovi_sample_backward_kernel<TG, M, P><<<grid, 256, 0, st>>>(a, (const TG*)grad_out, grad_img)
+#define RUN_T(TG)                                                                                          \
+  do {                                                                                                     \
+    if (mode == FOVI_NEAREST) { if (pad == FOVI_PAD_ZEROS) RUN(TG, FOVI_NEAREST, FOVI_PAD_ZEROS); else RUN(TG, FOVI_NEAREST, FOVI_PAD_BORDER); } \
+    else { if (pad == FOVI_PAD_ZEROS) RUN(TG, FOVI_BILINEAR, FOVI_PAD_ZEROS); else RUN(TG, FOVI_BILINEAR, FOVI_PAD_BORDER); }                  \
+  } while (0)
+  if (go_dtype == FOVI_F32) RUN_T(float); else RUN_T(__nv_bfloat16);
+#undef RUN_T
+#undef RUN
+  return fovi::after_launch("fovi_sample_backward_kernel");
 }

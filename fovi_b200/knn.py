@@ -228,15 +228,46 @@ class _DepthwiseBase(KNNConvLayer):
             self._packed["dw"] = (key, w.detach().float().permute(1, 0, 2).reshape(V, self.out_channels).contiguous())
         return self._packed["dw"][1]
 
-    def _check_no_grad(self, *tensors):
-        if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
-            raise RuntimeError("the depthwise layers implement the forward pass only: call them under torch.no_grad()")
+    @staticmethod
+    def _wants_grad(*tensors):
+        return torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors)
+
+
+class _DepthwiseFunction(torch.autograd.Function):
+    """Depthwise KNN convolution with its gradients (float32 atomics on the ordinary cores)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, layer):
+        ctx.layer, ctx.has_bias = layer, bias is not None
+        ctx.save_for_backward(x, weight)
+        with torch.no_grad():
+            return layer._plan.depthwise(x, layer._packed_depthwise(weight), bias)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, weight = ctx.saved_tensors
+        layer = ctx.layer
+        gx, gwp = layer._plan.depthwise_backward(x, layer._packed_depthwise(weight), gy, need_gx=ctx.needs_input_grad[0],
+                                                 need_gw=ctx.needs_input_grad[1])
+        gw = None
+        if gwp is not None:             # [V, C_in * g] -> [C_in, V, g]
+            V = gwp.shape[0]
+            gw = gwp.view(V, layer.in_channels, -1).permute(1, 0, 2).contiguous().to(weight.dtype)
+        gb = gy.sum((0, 2), dtype=torch.float32) if (ctx.has_bias and ctx.needs_input_grad[2]) else None
+        return (gx.to(x.dtype) if gx is not None else None), gw, gb, None
+
+
+class _Points:
+    """Stand-in for a coordinate set where only the point count matters."""
+
+    def __init__(self, n):
+        self.shape, self.dtype = (n, 2), torch.float32
 
 
 class KNNDepthwiseConvLayer(_DepthwiseBase):
     """Depthwise KNN convolution: every input channel is filtered on its own into g = out/in output channels
     (fovi/arch/knn.py:803-872).  Parameters as the reference: ``weight [C_in, V, g]``, ``bias [C_out]`` (a zero tensor
-    when bias=False).  forward(X [B,C_in,N_in]) -> [B,C_out,N_out]."""
+    when bias=False).  forward(X [B,C_in,N_in]) -> [B,C_out,N_out]; differentiable (input, filter and bias gradients)."""
 
     def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True, bias=False,
                  batch_size=None, ref_frame_side_length=None, **kwargs):
@@ -254,7 +285,8 @@ class KNNDepthwiseConvLayer(_DepthwiseBase):
         nn.init.uniform_(self.weight, a=-bound, b=bound)
 
     def forward(self, X_l):
-        self._check_no_grad(X_l, self.weight, self.bias)
+        if self._wants_grad(X_l, self.weight, self.bias):
+            return _DepthwiseFunction.apply(X_l, self.weight, self.bias, self)
         with torch.no_grad():
             return self._plan.depthwise(X_l, self._packed_depthwise(self.weight), self.bias)
 
@@ -280,6 +312,7 @@ class KNNDepthwiseSeparableConvLayer(_DepthwiseBase):
         if self.p_conv.bias is not None:
             nn.init.zeros_(self.p_conv.bias)
         n_out = self.knn_indices.shape[1]
+        self._pw_layer = None
         self._pw_plan = ops.KnnConvPlan(np.arange(n_out, dtype=np.int32)[None, :], np.zeros((n_out, 1), np.uint16), n_out, 1,
                                         out_channels, out_channels, device=dev)
 
@@ -291,8 +324,23 @@ class KNNDepthwiseSeparableConvLayer(_DepthwiseBase):
             self._packed[name] = (key, self._pw_plan.pack_weights(w.detach(), dtype))
         return self._packed[name][1]
 
+    def _pointwise_layer(self):
+        """The pointwise map as a KNNConv layer (every point its own only neighbour, one tap) that shares ``p_conv``'s
+        parameters: what the autograd path differentiates.  Kept out of the module tree so that state dicts are unchanged."""
+        if self._pw_layer is None:
+            n_out = self.knn_indices.shape[1]
+            L = KNNConvLayer(self.out_channels, self.out_channels, 1, _Points(n_out), _Points(n_out), device=self.device, bias=False,
+                             tables_override=dict(knn_indices=np.arange(n_out)[None, :], tap=np.zeros((n_out, 1), np.int64), V=1))
+            self._pw_layer = [L]
+        L = self._pw_layer[0]
+        L._parameters["weight"], L._parameters["bias"] = self.p_conv.weight, self.p_conv.bias
+        return L
+
     def forward(self, X_l):
-        self._check_no_grad(X_l, self.dw_conv, self.p_conv.weight)
+        if self._wants_grad(X_l, self.dw_conv, self.p_conv.weight, self.p_conv.bias):
+            from .grad import knnconv_autograd
+            dw = _DepthwiseFunction.apply(X_l, self.dw_conv, None, self)                  # [B, C_out, N_out]
+            return knnconv_autograd(self._pointwise_layer(), dw)
         with torch.no_grad():
             tc = X_l.dtype == torch.bfloat16 and self._pw_plan.tc_supported and self._pw_plan.x_layout == ops.X_BNC \
                 and self._pw_plan.cin_packed == self.out_channels

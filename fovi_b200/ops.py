@@ -128,6 +128,23 @@ def group_tables(idx, tap, n_in, G, max_list=256):
     return np.ascontiguousarray(uidx), utap, np.ascontiguousarray(mtap)
 
 
+def sample_backward(plan, grad_out, img_shape, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, layout=OUT_BFCN, grad_img=None):
+    """Gradient of `sample` with respect to the image.  grad_out [B,F,C,N] (or [F,B,C,N]) float32/bf16 -> float32
+    [B,C,H,W]; with `grad_img` given the gradient is accumulated into it."""
+    _need_cuda(grad_out, fix_rc, fix_hw)
+    B, Cc, H, W = img_shape
+    F = fix_rc.shape[1]
+    grad_out = grad_out.contiguous()
+    assert grad_out.shape == ((B, F, Cc, plan.n_points) if layout == OUT_BFCN else (F, B, Cc, plan.n_points)), grad_out.shape
+    if grad_img is None:
+        grad_img = torch.zeros((B, Cc, H, W), dtype=torch.float32, device=grad_out.device)
+    assert grad_img.dtype == torch.float32 and grad_img.is_contiguous() and tuple(grad_img.shape) == (B, Cc, H, W)
+    with torch.cuda.device(grad_out.device):
+        check(lib.fovi_sample_backward(plan._h, _ptr(grad_out), _dt(grad_out.dtype), layout, B, Cc, H, W, _ptr(fix_rc.to(torch.float32).contiguous()),
+                                       _ptr(fix_hw.to(torch.float32).contiguous()), F, mode, pad, _ptr(grad_img), _stream()), "fovi_sample_backward")
+    return grad_img
+
+
 class KnnConvPlan:
     """Device copy of one layer's compacted neighbour/tap tables (fovi_knnconv_plan)."""
 
@@ -291,6 +308,18 @@ class KnnConvPlan:
             check(lib.fovi_knn_depthwise_forward(self._h, _ptr(x), _dt(x.dtype), x_layout, _ptr(wp), _ptr(bias) if bias is not None else None,
                                                  _ptr(out), _dt(out.dtype), y_layout, B, int(relu), _stream()), "fovi_knn_depthwise_forward")
         return out
+
+    def depthwise_backward(self, x, wp, gy, x_layout=ACT_BCN, y_layout=ACT_BCN, need_gx=True, need_gw=True):
+        """Gradients of `depthwise`: returns (gX float32 in x's layout or None, gWp float32 [V, c_out] or None)."""
+        _need_cuda(x, wp, gy)
+        x, gy = x.contiguous(), gy.contiguous()
+        B = x.shape[0]
+        gx = torch.zeros(x.shape, dtype=torch.float32, device=x.device) if need_gx else None
+        gw = torch.zeros((self.V, self.c_out), dtype=torch.float32, device=x.device) if need_gw else None
+        with torch.cuda.device(x.device):
+            check(lib.fovi_knn_depthwise_backward(self._h, _ptr(x), _dt(x.dtype), x_layout, _ptr(wp), _ptr(gy), _dt(gy.dtype), y_layout, B,
+                                                  _ptr(gx) if need_gx else None, _ptr(gw) if need_gw else None, _stream()), "fovi_knn_depthwise_backward")
+        return gx, gw
 
     def check(self):
         """Synchronise the current stream and raise if a tensor-core launch gave up on a wait."""

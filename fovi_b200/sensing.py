@@ -66,6 +66,25 @@ def _as_bf2(v, B, device, what):
     return t.contiguous(), multi
 
 
+class _SampleFunction(torch.autograd.Function):
+    """sampler(img) with the image gradient of the reference (autograd through F.grid_sample, samplers.py:108); the
+    fixations carry no gradient."""
+
+    @staticmethod
+    def forward(ctx, img, fix_rc, fix_hw, sampler):
+        ctx.sampler, ctx.shape, ctx.in_dtype = sampler, tuple(img.shape), img.dtype
+        ctx.save_for_backward(fix_rc, fix_hw)
+        with torch.no_grad():
+            return sampler.sample(img, fix_rc, fix_hw)
+
+    @staticmethod
+    def backward(ctx, gy):
+        fix_rc, fix_hw = ctx.saved_tensors
+        s = ctx.sampler
+        g = ops.sample_backward(s._plan, gy, ctx.shape, fix_rc, fix_hw, mode=_MODES[s.mode], pad=_PADS[s.padding_mode])
+        return g.to(ctx.in_dtype), None, None, None
+
+
 class GridSampler(nn.Module):
     """Nearest / bilinear sampling of an image at the sensor's points around a fixation.
 
@@ -101,7 +120,10 @@ class GridSampler(nn.Module):
         fix_hw, _ = _as_bf2((H, W) if fixation_size is None else fixation_size, B, img.device, "fixation_size")
         if fix_hw.shape[1] != fix_rc.shape[1]:
             fix_hw = fix_hw.expand(B, fix_rc.shape[1], 2).contiguous()
-        out = self.sample(img, fix_rc, fix_hw)
+        if torch.is_grad_enabled() and img.requires_grad:
+            out = _SampleFunction.apply(img, fix_rc, fix_hw, self)
+        else:
+            out = self.sample(img, fix_rc, fix_hw)
         out = out if multi else out[:, 0]
         if return_coords:
             raise NotImplementedError("return_coords: the normalised grid is not materialised by the CUDA sampler")
@@ -158,9 +180,9 @@ class RetinalTransform(nn.Module):
             fixation_size = (fixation_size, fixation_size)
         return fix_loc, fixation_size
 
-    @torch.no_grad()
     def forward(self, x, fix_loc, fixation_size=None, **kwargs):
-        """x [B,C,H,W] -> [B,C,N] in ``self.dtype`` (retina.py:118-156); with fix_loc [B,F,2] -> [B,F,C,N]."""
+        """x [B,C,H,W] -> [B,C,N] in ``self.dtype`` (retina.py:118-156); with fix_loc [B,F,2] -> [B,F,C,N].  Differentiable
+        with respect to the images (the gradient kernel scatters onto the footprints with the forward's weights)."""
         fix_loc, fixation_size = self._defaults(fix_loc, fixation_size)
         return self.sampler(x, fix_loc=fix_loc, fixation_size=fixation_size).to(self.dtype)
 

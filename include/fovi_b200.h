@@ -105,6 +105,14 @@ int fovi_sample_forward(const fovi_sampler_plan* plan, const void* img, int dtyp
                         const int64_t* img_strides, const float* fix_rc, const float* fix_hw, int F, int mode,
                         int pad, void* out, int out_dtype, int layout, int out_channel_stride, void* stream);
 
+/* Gradient of fovi_sample_forward with respect to the image: what autograd through F.grid_sample gives
+ * the reference (samplers.py:108) when the images require grad.  grad_out: [B,F,C,N] (FOVI_OUT_BFCN) or
+ * [F,B,C,N] (FOVI_OUT_FBCN) of go_dtype; grad_img: float32 contiguous [B,C,H,W], ACCUMULATED into with
+ * atomic adds (zero it first for a plain gradient; the order of the additions is not fixed, so results
+ * agree with the reference to float32 rounding, not bit for bit).  Fixations carry no gradient. */
+int fovi_sample_backward(const fovi_sampler_plan* plan, const void* grad_out, int go_dtype, int layout, int B, int C, int H, int W,
+                         const float* fix_rc, const float* fix_hw, int F, int mode, int pad, float* grad_img, void* stream);
+
 /* Synchronises `stream` and returns FOVI_ERR_DEVICE_TIMEOUT if a sampler launch on this plan since the
  * last check gave up on the (bounded) wait for its asynchronous image copies; clears the word.  Such a
  * launch leaves its part of the output unwritten; nothing faults or hangs.  The reference has no
@@ -239,6 +247,13 @@ int fovi_sample_knnconv_fused(const fovi_sampler_plan* sampler, fovi_knnconv_pla
  * ------------------------------------------------------------------------------------------ */
 int fovi_knn_depthwise_forward(const fovi_knnconv_plan* plan, const void* X, int x_dtype, int x_layout, const float* Wp,
                                const float* bias, void* Y, int y_dtype, int y_layout, int B, int relu, void* stream);
+
+/* Gradients of fovi_knn_depthwise_forward (autograd through fovi/arch/knn.py:847-872).  gY: the output gradient in
+ * `y_layout` of g_dtype.  gX (may be NULL): float32 in X's layout, ACCUMULATED into (zero it first); needs Wp.
+ * gWp (may be NULL): float32 [V, c_out] in Wp's layout, ACCUMULATED into; needs X.  float32 atomics: sums agree with
+ * the reference to rounding.  The bias gradient is the plain sum of gY over rows and points. */
+int fovi_knn_depthwise_backward(const fovi_knnconv_plan* plan, const void* X, int x_dtype, int x_layout, const float* Wp, const void* gY,
+                                int g_dtype, int y_layout, int B, float* gX, float* gWp, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Backward pass of KNNConv.  The reference gets its gradients from autograd through gather, one-hot matmul and linear

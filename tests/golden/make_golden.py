@@ -209,8 +209,49 @@ def depthwise_fixture(save, knn):
     o2 = np.einsum("bcn,oc->bon", o2, pw) + pb[None, :, None]
     assert rel_err(o2, ys) < 1e-5, rel_err(o2, ys)
     out["dwsep_out"] = ys
+    # gradients of both layers (autograd through the same steps) for a seeded output gradient
+    def steps_t(layer, xt, wt):
+        f = layer._apply_local_rf(layer._pad_and_gather_knns(xt))
+        f = rearrange(f, "b n (d v) -> b n d v", d=16)
+        return torch.einsum("bndv,dvg->bndg", f, wt).reshape(xt.shape[0], f.shape[1], -1)
+    gy = np.random.RandomState(43).standard_normal(y.shape).astype(f32)
+    out["gy"] = gy
+    with torch.enable_grad():
+        xt, wt, bt = (torch.from_numpy(a).clone().requires_grad_() for a in (x, w, b))
+        yy = steps_t(dw, xt, wt).transpose(1, 2) + bt[None, :, None]
+        (yy * torch.from_numpy(gy)).sum().backward()
+        out["dw_dX"], out["dw_dW"], out["dw_db"] = xt.grad.numpy(), wt.grad.numpy(), bt.grad.numpy()
+        xt, wt = (torch.from_numpy(a).clone().requires_grad_() for a in (x, w))
+        sep.p_conv.weight.requires_grad_(True); sep.p_conv.bias.requires_grad_(True)
+        sep.p_conv.weight.grad = None; sep.p_conv.bias.grad = None
+        yy = sep.p_conv(steps_t(sep, xt, wt)).transpose(1, 2)
+        (yy * torch.from_numpy(gy)).sum().backward()
+        out["dwsep_dX"], out["dwsep_dW"] = xt.grad.numpy(), wt.grad.numpy()
+        out["dwsep_dPW"], out["dwsep_dPb"] = sep.p_conv.weight.grad.numpy().copy(), sep.p_conv.bias.grad.numpy().copy()
     save("depthwise_small.npz", **out)
     print("depthwise fixture: n_in", len(ic), "n_out", len(oc), "V", V, "state keys", sorted(sep.state_dict().keys()), sorted(dw.state_dict().keys()))
+
+
+def sampler_backward_fixture(save, retina):
+    """Image gradient of the reference sensor (autograd through F.grid_sample, samplers.py:108) on CPU."""
+    rt = retina.RetinalTransform(resolution=20, start_res=48, fov=16, cmf_a=1.0, style="isotropic", sampler="grid_bilinear", fixation_size=48,
+                                 auto_match_cart_resources=0, device="cpu")
+    rs = np.random.RandomState(61)
+    B, F = 2, 3
+    x = rs.random_sample((B, 3, 48, 48)).astype(f32)
+    fix = (-0.1 + 1.2 * rs.random_sample((B, F, 2))).astype(f32)
+    N = len(rt.sampler.coords)
+    gy = rs.standard_normal((B, F, 3, N)).astype(f32)
+    out = {"seed": np.int64(61), "fix": fix, "sampling_grid": rt.sampler.sampling_grid.numpy()[0, 0]}
+    for mode in ("bilinear", "nearest"):
+        rt.sampler.mode = mode
+        with torch.enable_grad():
+            xt = torch.from_numpy(x).clone().requires_grad_()
+            ys = torch.stack([rt(xt, torch.from_numpy(fix[:, f])) for f in range(F)], 1)          # [B,F,C,N]
+            (ys * torch.from_numpy(gy)).sum().backward()
+        out[f"{mode}_y"], out[f"{mode}_dx"] = ys.detach().numpy(), xt.grad.numpy()
+    save("sampler_backward_small.npz", **out)
+    print("sampler backward fixture: N", N)
 
 
 def norms_fixture(save, knn):
@@ -252,7 +293,7 @@ def norms_fixture(save, knn):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
-    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise", "norms"], help="regenerate one fixture group only")
+    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise", "norms", "sampler_backward"], help="regenerate one fixture group only")
     args = ap.parse_args()
     knn, retina, coords, knnvit = load_reference(args.reference)
     torch.set_grad_enabled(False)
@@ -265,6 +306,8 @@ def main():
         return depthwise_fixture(save, knn)
     if args.only == "norms":
         return norms_fixture(save, knn)
+    if args.only == "sampler_backward":
+        return sampler_backward_fixture(save, retina)
 
     # ------------------------------------------------------------ sensors (geometry fixtures)
     sensors = {}
@@ -434,6 +477,7 @@ def main():
     backward_fixture(save, knn)
     depthwise_fixture(save, knn)
     norms_fixture(save, knn)
+    sampler_backward_fixture(save, retina)
 
 
 if __name__ == "__main__":

@@ -60,8 +60,8 @@ def test_depthwise_matches_reference_steps(golden):
         nb.weight.copy_(torch.from_numpy(w))
         y0 = nb(torch.from_numpy(x).cuda())
     assert rel_max(y0.cpu().numpy(), g["dw_out"] - b[None, :, None]) < 1e-5
-    with torch.enable_grad(), pytest.raises(RuntimeError):
-        layer(torch.from_numpy(x).cuda())                           # gradients enabled: forward only
+    with torch.enable_grad():
+        assert layer(torch.from_numpy(x).cuda()).grad_fn is not None    # gradients enabled: differentiable (see the gradient test)
 
 
 def test_depthwise_separable_matches_reference_steps(golden):
@@ -84,3 +84,38 @@ def test_depthwise_separable_matches_reference_steps(golden):
     err = np.linalg.norm(yb.float().cpu().numpy() - g["dwsep_out"]) / np.linalg.norm(g["dwsep_out"])
     assert err < 1e-2, err
     layer._pw_plan.check()
+
+
+@pytest.mark.autograd
+def test_depthwise_gradients_match_reference_autograd(golden):
+    """Input, filter and bias gradients of the depthwise layer, and all four parameter/input gradients of the separable
+    layer, against autograd through the reference layers' own steps (float32 scatter-adds: 1e-4; the separable layer's
+    pointwise map runs in bf16 on the tensor cores: 1e-2 relative L2)."""
+    from fovi_b200.knn import KNNDepthwiseConvLayer, KNNDepthwiseSeparableConvLayer
+    g = golden("depthwise_small.npz")
+    x, w, b, pw, pb = _inputs(g)
+    gy = torch.from_numpy(g["gy"]).cuda()
+    rel = lambda a, r: float(np.linalg.norm(a - r) / max(np.linalg.norm(r), 1e-30))  # noqa: E731
+    layer = _make(KNNDepthwiseConvLayer, g, bias=True)
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(w)); layer.bias.copy_(torch.from_numpy(b))
+    xt = torch.from_numpy(x).cuda().requires_grad_()
+    y = layer(xt)
+    assert rel_max(y.detach().cpu().numpy(), g["dw_out"]) < 1e-5
+    (y * gy).sum().backward()
+    assert rel(xt.grad.cpu().numpy(), g["dw_dX"]) < 1e-4
+    assert rel(layer.weight.grad.cpu().numpy(), g["dw_dW"]) < 1e-4
+    assert rel(layer.bias.grad.cpu().numpy(), g["dw_db"]) < 1e-4
+    sep = _make(KNNDepthwiseSeparableConvLayer, g, bias=True)
+    with torch.no_grad():
+        sep.dw_conv.copy_(torch.from_numpy(w)); sep.p_conv.weight.copy_(torch.from_numpy(pw)); sep.p_conv.bias.copy_(torch.from_numpy(pb))
+    keys = sorted(sep.state_dict().keys())
+    xt = torch.from_numpy(x).cuda().requires_grad_()
+    y = sep(xt)
+    assert sorted(sep.state_dict().keys()) == keys                      # the helper layer stays out of the module tree
+    assert rel(y.detach().float().cpu().numpy(), g["dwsep_out"]) < 1e-2
+    (y * gy).sum().backward()
+    assert rel(xt.grad.cpu().numpy(), g["dwsep_dX"]) < 2e-2
+    assert rel(sep.dw_conv.grad.cpu().numpy(), g["dwsep_dW"]) < 2e-2
+    assert rel(sep.p_conv.weight.grad.cpu().numpy(), g["dwsep_dPW"]) < 1e-2
+    assert rel(sep.p_conv.bias.grad.cpu().numpy(), g["dwsep_dPb"]) < 1e-2

@@ -194,3 +194,36 @@ def test_strip_kernel_cases(ops, golden, mode, pad):
     x = synth_images(4, (2, 3, 50, 96))
     ref = oracle.retinal_sample(x[..., 16:80], grid, fix, hw, mode, pad)
     assert np.array_equal(ops.sample(plan, dev(x)[..., 16:80], dev(fix), dev(hw), mode=m, pad=p).cpu().numpy(), ref)
+
+
+@pytest.mark.autograd
+@pytest.mark.parametrize("mode", ["bilinear", "nearest"])
+def test_image_gradient_matches_reference_autograd(ops, golden, mode):
+    """d(sum(y * gy))/d(image) through the module API against the gradient the reference's sensor produced on CPU
+    (autograd through F.grid_sample).  Atomic float32 accumulation: equal to rounding, not bit for bit."""
+    from fovi_b200.sensing import GridSampler
+    from fovi_b200.coords import SamplingCoords
+    g = golden("sampler_backward_small.npz")
+    rs = np.random.RandomState(int(g["seed"]))
+    B, F = 2, 3
+    x = rs.random_sample((B, 3, 48, 48)).astype(f32)
+    fix = (-0.1 + 1.2 * rs.random_sample((B, F, 2))).astype(f32)
+    assert np.array_equal(fix, g["fix"])
+    N = g["sampling_grid"].shape[0]
+    gy = rs.standard_normal((B, F, 3, N)).astype(f32)
+    sampler = GridSampler(16, 1.0, 20, device="cuda", mode=mode, coords=SamplingCoords(16, 1.0, 20, device="cuda"))
+    assert np.array_equal(sampler.sampling_grid[0, 0].cpu().numpy(), g["sampling_grid"])
+    xt = dev(x).requires_grad_()
+    y = sampler(xt, dev(fix), (48, 48))
+    assert y.requires_grad and np.array_equal(y.detach().cpu().numpy(), g[f"{mode}_y"])
+    (y * dev(gy)).sum().backward()
+    ref = g[f"{mode}_dx"]
+    assert np.abs(xt.grad.cpu().numpy() - ref).max() < 1e-5 * max(1.0, np.abs(ref).max())
+    # the plain C entry point, [F,B,C,N] layout and bf16 gradients, accumulating into an existing buffer
+    acc = torch.ones((B, 3, 48, 48), device="cuda")
+    hw = torch.full((B, F, 2), 48.0, device="cuda")
+    gyb = dev(gy).to(torch.bfloat16)
+    ops.sample_backward(sampler._plan, gyb.permute(1, 0, 2, 3).contiguous(), (B, 3, 48, 48), dev(fix), hw, mode=ops.BILINEAR if mode == "bilinear" else ops.NEAREST,
+                        layout=ops.OUT_FBCN, grad_img=acc)
+    want = ops.sample_backward(sampler._plan, gyb.float(), (B, 3, 48, 48), dev(fix), hw, mode=ops.BILINEAR if mode == "bilinear" else ops.NEAREST) + 1
+    assert float((acc - want).abs().max()) < 1e-4
