@@ -9,8 +9,8 @@ A step = one pass of the hot path over one batch: `--batch` images of 3x256x256 
 -> KNNConv 3->64->192->384->256->256 with ReLU between layers (bf16 operands, fp32 accumulation).
 `value` is image x fixations per second with the images resident in HBM; `e2e` is the same metric
 through the public module API with pinned HOST images in and the final activations copied back to the
-host inside the timed region (`e2e_bf16_in`: the same with bf16 host images; `e2e_copy_floor_ms`: the
-copies alone).  With N > 1 every rank runs its own batch (weak scaling, no collective on the path); times
+host inside the timed region (`e2e_bf16_in` / `e2e_u8_in`: the same with bf16 / uint8 host images;
+`e2e_copy_floor_ms`: the copies alone).  With N > 1 every rank runs its own batch (weak scaling, no collective on the path); times
 are the max over ranks; the one collective the path has, the all-gather of final outputs, is timed
 separately after the loop.  `extras` (one GPU) holds the other workloads of the task: the sampler sweep,
 the exact float32 layer, the patch embeddings, a training step, the shipped AlexNet backbone, and the
@@ -497,6 +497,7 @@ def main():
     rs = np.random.RandomState(1000 + rank)
     x_host = torch.from_numpy(rs.random_sample((B, 3, 256, 256)).astype(np.float32)).pin_memory()
     x_host16 = x_host.to(torch.bfloat16).pin_memory()
+    x_host8 = (x_host * 255).round().to(torch.uint8).pin_memory()      # what a data loader holds before its float conversion
     fix_host = torch.from_numpy((0.25 + 0.5 * rs.random_sample((B, F, 2))).astype(np.float32)).pin_memory()
     x_dev, fix_dev = x_host.to(dev), fix_host.to(dev)
     out_host = torch.empty((B, F, plans[-1].n_out, CHANS[-1]), dtype=torch.bfloat16).pin_memory()
@@ -566,6 +567,11 @@ def main():
     e2e16_matches = bool(torch.equal(y16.permute(1, 0, 2, 3).cpu(), out_host))
     ms_floor16, _, _ = timed(lambda _r: front.run_from_host(x_host16, fix_host, out_host, chunks=args.chunks, kernels=False), min(args.steps, 20), 2)
     del y16
+    ms_e2e8, _, per_e2e8 = timed(lambda _r: front.run_from_host(x_host8, fix_host, out_host, chunks=args.chunks), args.steps, 3)
+    y8 = front.forward(x_host8.to(dev), fix_dev).view(F, B, plans[-1].n_out, CHANS[-1])
+    torch.cuda.synchronize()
+    e2e8_matches = bool(torch.equal(y8.permute(1, 0, 2, 3).cpu(), out_host))
+    del y8
 
     # ---- the one collective of the path (N > 1): all-gather of the final outputs, and of a [rows, 1280] bf16 block shaped
     # like the CLS embeddings of the ViT-H configuration; verified, timed apart from `value`
@@ -663,6 +669,7 @@ def main():
         value = world * M * args.steps / (ms_total * 1e-3)
         e2e = world * M * args.steps / (ms_e2e * 1e-3)
         e2e16 = world * M * args.steps / (ms_e2e16 * 1e-3)
+        e2e8 = world * M * args.steps / (ms_e2e8 * 1e-3)
         fresh = NCU_DRAM_TRAFFIC_MB["sources"] == kernel_sources_hash() and (B, F) == NCU_DRAM_TRAFFIC_MB["workload"] and NCU_DRAM_TRAFFIC_MB["conv"]
         floor_steps = min(args.steps, 20)
         line = {
@@ -689,6 +696,9 @@ def main():
             "e2e_bf16_in": {"value": e2e16, "unit": UNIT, "h2d_bytes_per_step": x_host16.numel() * 2 + fix_host.numel() * 4,
                             "d2h_bytes_per_step": out_host.numel() * 2, "ms_per_step": ms_e2e16 / args.steps, "ms_per_step_spread": spread(per_e2e16),
                             "matches_device_path": e2e16_matches, "input": "bfloat16 host images"},
+            "e2e_u8_in": {"value": e2e8, "unit": UNIT, "h2d_bytes_per_step": x_host8.numel() + fix_host.numel() * 4, "d2h_bytes_per_step": out_host.numel() * 2,
+                          "ms_per_step": ms_e2e8 / args.steps, "ms_per_step_spread": spread(per_e2e8), "matches_device_path": e2e8_matches,
+                          "input": "uint8 host images (sampled as the float32 values 0..255 they hold)"},
             "e2e_copy_floor_ms": {"float32_in": ms_floor / floor_steps, "bf16_in": ms_floor16 / floor_steps,
                                   "note": "the same chunks, streams and dependencies with the kernels left out: what the host<->device copies cost "
                                           "on this machine; per-rank GB/s = (h2d + d2h bytes) / this",

@@ -45,6 +45,7 @@ template <> __device__ __forceinline__ float ld_as_float<float>(const float* p) 
 template <> __device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16* p) {
   return __bfloat162float(__ldg(p));
 }
+template <> __device__ __forceinline__ float ld_as_float<unsigned char>(const unsigned char* p) { return (float)__ldg(p); }
 template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }

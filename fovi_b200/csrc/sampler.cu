@@ -113,6 +113,7 @@ __device__ __forceinline__ float tap(const TIn* plane, long long sy, long long s
 template <typename T> __device__ __forceinline__ float smem_as_float(const T* p);
 template <> __device__ __forceinline__ float smem_as_float<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float smem_as_float<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <> __device__ __forceinline__ float smem_as_float<unsigned char>(const unsigned char* p) { return (float)*p; }
 
 // ------------------------------------------------------------------------------------------------------------
 // Strip kernel.
@@ -796,7 +797,7 @@ extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* im
   if (!plan || !img_strides) return FOVI_ERR_INVALID_ARGUMENT;
   if (B > 0 && (!img || !fix_rc || !fix_hw || !out)) return FOVI_ERR_INVALID_ARGUMENT;
   if (B < 0 || C <= 0 || H <= 0 || W <= 0 || F <= 0) return FOVI_ERR_INVALID_ARGUMENT;
-  if (!fovi::valid_dtype(dtype) || !fovi::valid_dtype(out_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
+  if ((!fovi::valid_dtype(dtype) && dtype != FOVI_U8) || !fovi::valid_dtype(out_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   if (mode != FOVI_NEAREST && mode != FOVI_BILINEAR) return FOVI_ERR_INVALID_ARGUMENT;
   if (pad != FOVI_PAD_ZEROS && pad != FOVI_PAD_BORDER) return FOVI_ERR_INVALID_ARGUMENT;
   if (layout < FOVI_OUT_BFCN || layout > FOVI_OUT_BF_PAIRS) return FOVI_ERR_INVALID_ARGUMENT;
@@ -823,6 +824,8 @@ extern "C" int fovi_sample_forward(const fovi_sampler_plan* plan, const void* im
   a.R = a.n_strips = a.pitch = a.layout = a.full_rows = 0;
   a.rank_lut = plan->rank_lut; a.lut_scale = plan->lut_scale; a.status = plan->status;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == FOVI_U8 && out_dtype == FOVI_F32) return dispatch_mode<unsigned char, float>(a, mode, pad, nc, st);
+  if (dtype == FOVI_U8) return dispatch_mode<unsigned char, __nv_bfloat16>(a, mode, pad, nc, st);
   if (dtype == FOVI_F32 && out_dtype == FOVI_F32) return dispatch_mode<float, float>(a, mode, pad, nc, st);
   if (dtype == FOVI_F32 && out_dtype == FOVI_BF16) return dispatch_mode<float, __nv_bfloat16>(a, mode, pad, nc, st);
   if (dtype == FOVI_BF16 && out_dtype == FOVI_BF16) return dispatch_mode<__nv_bfloat16, __nv_bfloat16>(a, mode, pad, nc, st);

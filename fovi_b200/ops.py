@@ -7,7 +7,7 @@ import torch
 
 from ._lib import lib, check
 
-F32, BF16 = 0, 1
+F32, BF16, U8 = 0, 1, 2
 NEAREST, BILINEAR = 0, 1
 PAD_ZEROS, PAD_BORDER = 0, 1
 OUT_BFCN, OUT_FBCN, OUT_BFNC, OUT_FBNC, OUT_FB_PAIRS, OUT_BF_PAIRS = 0, 1, 2, 3, 4, 5
@@ -62,7 +62,8 @@ class SamplerPlan:
 
 
 def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=None, layout=OUT_BFCN, channel_stride=None, out=None):
-    """img [B,C,H,W] (any strides); fix_rc, fix_hw [B,F,2] float32 CUDA.  Returns the sampled
+    """img [B,C,H,W] (any strides; float32, bfloat16, or uint8 sampled as the float32 values it holds);
+    fix_rc, fix_hw [B,F,2] float32 CUDA.  Returns the sampled
     tensor in `layout`: [B,F,C,N], [F,B,C,N], [B,F,N,Cp], [F,B,N,Cp], or the pair layout
     [ceil(rows/128), ceil(N/2), 128, 8] (rows = F*B or B*F) that a KNNConv plan with c_in <= 4
     consumes; rows past the last one are left unwritten."""
@@ -72,7 +73,8 @@ def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=No
     fix_hw = fix_hw.to(torch.float32).contiguous()
     F = fix_rc.shape[1]
     assert fix_rc.shape == (B, F, 2) and fix_hw.shape == (B, F, 2)
-    out_dtype = img.dtype if out_dtype is None else out_dtype
+    if out_dtype is None:
+        out_dtype = torch.float32 if img.dtype == torch.uint8 else img.dtype
     nc = layout in (OUT_BFNC, OUT_FBNC)
     pairs = layout in (OUT_FB_PAIRS, OUT_BF_PAIRS)
     cp = (channel_stride or Cc) if nc else Cc
@@ -88,7 +90,7 @@ def sample(plan, img, fix_rc, fix_hw, mode=BILINEAR, pad=PAD_ZEROS, out_dtype=No
         assert out.shape == shape and out.dtype == out_dtype and out.is_contiguous()
     strides = (C.c_int64 * 4)(*img.stride())
     with torch.cuda.device(img.device):
-        check(lib.fovi_sample_forward(plan._h, _ptr(img), _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc), _ptr(fix_hw), F,
+        check(lib.fovi_sample_forward(plan._h, _ptr(img), U8 if img.dtype == torch.uint8 else _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc), _ptr(fix_hw), F,
                                       mode, pad, _ptr(out), _dt(out_dtype), layout, cp, _stream()), "fovi_sample_forward")
     return out
 

@@ -33,7 +33,7 @@ typedef enum {
   FOVI_ERR_NO_DEVICE = 7         /* no sm_100 device is current                                */
 } fovi_status;
 
-typedef enum { FOVI_F32 = 0, FOVI_BF16 = 1 } fovi_dtype;
+typedef enum { FOVI_F32 = 0, FOVI_BF16 = 1, FOVI_U8 = 2 /* sampler images only */ } fovi_dtype;
 typedef enum { FOVI_NEAREST = 0, FOVI_BILINEAR = 1 } fovi_sample_mode;
 typedef enum { FOVI_PAD_ZEROS = 0, FOVI_PAD_BORDER = 1 } fovi_pad_mode;
 
@@ -92,7 +92,9 @@ void fovi_sampler_plan_destroy(fovi_sampler_plan* plan);
 int fovi_sampler_plan_num_points(const fovi_sampler_plan* plan);
 
 /* img        : [B,C,H,W] elements of `dtype`, element strides img_strides[4] (any NCHW or
- *              NHWC-strided view; no overlap).
+ *              NHWC-strided view; no overlap).  FOVI_U8 images (what a data loader hands over before
+ *              its float conversion) are sampled as the float32 values 0..255 they hold, i.e. the
+ *              result is the reference's on img.float(); a quarter of the float32 bytes cross PCIe.
  * fix_rc     : DEVICE [B,F,2] float32, normalised fixation centre (row, col)
  *              — RetinalTransform._check_fix_loc, retina.py:211-237.
  * fix_hw     : DEVICE [B,F,2] float32, fixation size in pixels (height, width)

@@ -129,6 +129,22 @@ def test_edge_cases(ops, golden):
     assert torch.equal(a, b)
 
 
+def test_uint8_images(ops, golden):
+    """uint8 images are sampled as the float32 values they hold: the reference's result on img.float(), bit for bit, on
+    both kernels (aligned rows: the strip kernel; a 50-pixel-wide image: the general one)."""
+    grid = golden("sensor_a1.npz")["sampling_grid"]
+    plan = ops.SamplerPlan(grid)
+    rs = np.random.RandomState(21)
+    for H, W in ((64, 96), (40, 50)):
+        x8 = rs.randint(0, 256, (2, 3, H, W)).astype(np.uint8)
+        fix = (0.1 + 0.8 * rs.random_sample((2, 2, 2))).astype(f32); hw = np.full((2, 2, 2), 60, f32)
+        ref = oracle.retinal_sample(x8.astype(f32), grid, fix, hw)
+        y = ops.sample(plan, dev(x8), dev(fix), dev(hw))
+        assert y.dtype == torch.float32 and np.array_equal(y.cpu().numpy(), ref)
+        yb = ops.sample(plan, dev(x8), dev(fix), dev(hw), out_dtype=torch.bfloat16)
+        assert torch.equal(yb.cpu(), torch.from_numpy(ref).to(torch.bfloat16))
+
+
 def _pairs_to_rows(y, rows, N):
     """Pair layout [tiles, ceil(N/2), 128, 8] -> float32 [rows, N, 4]."""
     t = y.to(torch.float32).cpu().numpy()
