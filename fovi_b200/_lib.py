@@ -40,7 +40,7 @@ SIGNATURES = {
     "fovi_knnconv_forward_bcn_static": (C.c_int, [_P, _P, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_fused_intermediate_bytes": (C.c_int64, [_P, C.c_int]),
     "fovi_sample_knnconv_fused": (C.c_int, [_P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), _P, _P,
-                                            C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.c_int, C.c_int, _P]),
+                                            C.c_int, C.c_int, C.c_int, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knnconv_pack_weights_grouped": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_knn_depthwise_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knn_depthwise_backward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),

@@ -332,8 +332,9 @@ class KnnConvPlan:
 
 
 def sample_knnconv_fused(splan, cplan, img, fix_rc, fix_hw, wt, bias=None, relu=False, mode=BILINEAR, pad=PAD_ZEROS,
-                         out_dtype=torch.bfloat16, intermediate=None, out=None):
-    """Sensor -> first KNNConv in one C call.  Returns ([F*B, n_out, c_out], intermediate buffer)."""
+                         out_dtype=torch.bfloat16, intermediate=None, out=None, row_order="fb"):
+    """Sensor -> first KNNConv in one C call, the sensor output held in L2 between the two kernels.  Rows '(f b)' or, with
+    row_order "bf", '(b f)'.  Returns ([rows, n_out, c_out], intermediate buffer)."""
     _need_cuda(img, fix_rc, fix_hw, wt, bias)
     B, Cc, H, W = img.shape
     F = fix_rc.shape[1]
@@ -347,9 +348,10 @@ def sample_knnconv_fused(splan, cplan, img, fix_rc, fix_hw, wt, bias=None, relu=
         bias = cplan._tc_bias(bias).detach().to(torch.float32).contiguous()
     strides = (C.c_int64 * 4)(*img.stride())
     with torch.cuda.device(img.device):
-        check(lib.fovi_sample_knnconv_fused(splan._h, cplan._h_tc, _ptr(img), _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc.contiguous()),
+        check(lib.fovi_sample_knnconv_fused(splan._h, cplan._h_tc, _ptr(img), U8 if img.dtype == torch.uint8 else _dt(img.dtype), B, Cc, H, W, strides, _ptr(fix_rc.contiguous()),
                                             _ptr(fix_hw.contiguous()), F, mode, pad, _ptr(intermediate), _ptr(wt),
-                                            _ptr(bias) if bias is not None else None, _ptr(out), _dt(out.dtype), int(relu), _stream()),
+                                            _ptr(bias) if bias is not None else None, _ptr(out), _dt(out.dtype), int(relu),
+                                            {"fb": 0, "bf": 1}[row_order], _stream()),
               "fovi_sample_knnconv_fused")
     return out, intermediate
 

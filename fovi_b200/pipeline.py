@@ -13,6 +13,8 @@ fixations of an image together), so that a chunk of images is one contiguous blo
 """
 import torch
 
+from . import ops
+
 __all__ = ["FoveatedFrontEnd"]
 
 
@@ -50,12 +52,26 @@ class FoveatedFrontEnd:
         the slot's).  `between(i)` is called after launch i (0 = sensor, 1.. = layers): the benchmark records events there."""
         B, F = fix.shape[0], fix.shape[1]
         rows = B * F
-        xp, _ = self.retina.forward_points(img, fix, fixation_size, conv_plan=self.first_plan, out=slot["s_out"], row_order=row_order)
-        if between:
-            between(0)
-        h = xp
         n = len(self.stack.layers)
+        L0 = self.stack.layers[0]
+        first = 0
+        if between is None and L0.plan.tc_supported:
+            # sensor and first layer through the fused entry point: the sensor output is handed over in L2
+            sampler = self.retina.sampler
+            fix_rc, fix_hw = self.retina.fixation_tensors(img, fix, fixation_size)
+            dst = out if (out is not None and n == 1) else slot["acts"][0]
+            h, _ = ops.sample_knnconv_fused(sampler._plan, L0.plan, img, fix_rc, fix_hw, L0.packed_weight(), L0.bias, relu=(n > 1) or self.stack.final_relu,
+                                            mode=ops.BILINEAR if sampler.mode == "bilinear" else ops.NEAREST,
+                                            pad=ops.PAD_ZEROS if sampler.padding_mode == "zeros" else ops.PAD_BORDER,
+                                            out_dtype=dst.dtype, intermediate=slot["s_out"], out=dst, row_order=row_order)
+            first = 1
+        else:
+            h, _ = self.retina.forward_points(img, fix, fixation_size, conv_plan=self.first_plan, out=slot["s_out"], row_order=row_order)
+            if between:
+                between(0)
         for i, L in enumerate(self.stack.layers):
+            if i < first:
+                continue
             dst = out if (out is not None and i == n - 1) else slot["acts"][i]
             h = L.forward_points(h, batch=rows, relu=(i < n - 1) or self.stack.final_relu, out_dtype=dst.dtype, out=dst)
             if between:

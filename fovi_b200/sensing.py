@@ -194,13 +194,9 @@ class RetinalTransform(nn.Module):
         what a pipeline cutting the batch into chunks of images wants).  Returns (tensor, rows)."""
         if row_order not in ("fb", "bf"):
             raise ValueError("row_order must be 'fb' or 'bf'")
-        B, _, H, W = x.shape
-        fix_loc, fixation_size = self._defaults(fix_loc, fixation_size)
-        fix_rc, _ = _as_bf2(fix_loc, B, x.device, "fix_loc")
-        fix_hw, _ = _as_bf2(fixation_size, B, x.device, "fixation_size")
+        B = x.shape[0]
+        fix_rc, fix_hw = self.fixation_tensors(x, fix_loc, fixation_size)
         F = fix_rc.shape[1]
-        if fix_hw.shape[1] != F:
-            fix_hw = self._expanded(fix_hw, B, F)
         fb = row_order == "fb"
         if conv_plan is not None and conv_plan.x_layout == ops.X_PAIRS:
             y = self.sampler.sample(x, fix_rc, fix_hw, layout=ops.OUT_FB_PAIRS if fb else ops.OUT_BF_PAIRS, out=out)
@@ -209,6 +205,16 @@ class RetinalTransform(nn.Module):
             y = self.sampler.sample(x, fix_rc, fix_hw, out_dtype=torch.bfloat16, layout=ops.OUT_FBNC if fb else ops.OUT_BFNC, channel_stride=cp, out=out)
             y = y.reshape(F * B, y.shape[2], cp)
         return y, F * B
+
+    def fixation_tensors(self, x, fix_loc, fixation_size=None):
+        """(centres, sizes) as the kernels take them: float32 [B,F,2] on x's device, defaults filled in."""
+        B = x.shape[0]
+        fix_loc, fixation_size = self._defaults(fix_loc, fixation_size)
+        fix_rc, _ = _as_bf2(fix_loc, B, x.device, "fix_loc")
+        fix_hw, _ = _as_bf2(fixation_size, B, x.device, "fixation_size")
+        if fix_hw.shape[1] != fix_rc.shape[1]:
+            fix_hw = self._expanded(fix_hw, B, fix_rc.shape[1])
+        return fix_rc, fix_hw
 
     def _expanded(self, fix_hw, B, F):
         """[B,1,2] -> contiguous [B,F,2]; the result for a cached constant is cached too."""

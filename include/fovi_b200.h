@@ -231,14 +231,17 @@ int fovi_knnconv_check(fovi_knnconv_plan* plan, void* stream);
 /* Sensor -> first KNNConv in one call (the multi-fixation loop of policies.py:266-277 followed by the
  * first KNNConvLayer.forward of the backbone, knnalexnet.py:118-119): samples all F fixations straight
  * into the layout `conv` consumes, in `intermediate` (caller-owned device scratch of
- * fovi_fused_intermediate_bytes(conv, B*F) bytes; it stays L2 resident between the two kernels), then runs
- * the tensor-core layer.  Output rows are ordered '(f b)'.  Requires the sampler's point count == conv's
- * n_in and C == conv's c_in.  Other arguments as for fovi_sample_forward / fovi_knnconv_forward. */
+ * fovi_fused_intermediate_bytes(conv, B*F) bytes), then runs the tensor-core layer.  For the two launches
+ * the intermediate is held in L2 through the stream's access-policy window (persisting for the sampler's
+ * writes, released by the convolution's reads), so the sensor output makes no round trip through HBM; the
+ * window is cleared before the call returns.  row_order 0: output rows '(f b)' (fovi/fovinet.py:281),
+ * 1: '(b f)'.  Requires the sampler's point count == conv's n_in and C == conv's c_in.  Other arguments as
+ * for fovi_sample_forward / fovi_knnconv_forward. */
 int64_t fovi_fused_intermediate_bytes(const fovi_knnconv_plan* conv, int rows);
 int fovi_sample_knnconv_fused(const fovi_sampler_plan* sampler, fovi_knnconv_plan* conv, const void* img, int dtype, int B,
                               int C, int H, int W, const int64_t* img_strides, const float* fix_rc, const float* fix_hw,
                               int F, int mode, int pad, void* intermediate, const void* Wt, const float* bias, void* Y,
-                              int y_dtype, int relu, void* stream);
+                              int y_dtype, int relu, int row_order, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Depthwise KNN convolution: out[b, c*g + j, n] = bias[c*g + j] + sum_k Xpad[b, c, idx[k,n]] * W[c, tap[n,k], j],

@@ -134,6 +134,15 @@ def test_fused_sample_knnconv_call_equals_two_calls(golden):
     want = cplan.forward(xin, wt, relu=True, out_dtype=torch.float32, batch=B * F)
     cplan.check()
     assert y.shape == (B * F, 3975, 64) and torch.equal(y, want)
+    # ... and against the oracle: sampler bit-exact, rounded to bf16 like the intermediate, then the layer on bf16 operands
+    w = kaiming_weight(np.random.RandomState(1), 64, 3, V)
+    xs = oracle.retinal_sample(x.cpu().numpy(), s["sampling_grid"], fix.cpu().numpy(), hw.cpu().numpy())            # [B,F,C,N]
+    xs = torch.from_numpy(xs).to(torch.bfloat16).float().numpy().transpose(1, 0, 2, 3).reshape(B * F, 3, -1)[:4]
+    wr = torch.from_numpy(w).to(torch.bfloat16).float().numpy()
+    ref = oracle.knnconv_forward_closed_form(xs, g["knn_idx_pad"], g["tap"].astype(np.int64), V, wr, relu=True)
+    assert np.abs(y[:4].permute(0, 2, 1).cpu().numpy() - ref).max() < 2e-3 * max(1.0, np.abs(ref).max())
+    yb, _ = ops.sample_knnconv_fused(splan, cplan, x, fix, hw, wt, relu=True, out_dtype=torch.float32, row_order="bf")
+    assert torch.equal(yb.view(B, F, 3975, 64), y.view(F, B, 3975, 64).permute(1, 0, 2, 3))
 
 
 @pytest.mark.parametrize("name,kw,train", [

@@ -18,6 +18,7 @@ import pytest
 import torch
 
 from conftest import synth_images, kaiming_weight
+from oracle import fovi_oracle as oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -35,7 +36,7 @@ def _static_forward(lib, plan, x, wt, bias, relu):
     return y
 
 
-def _check_two_calls(ops, lib, plan, w, c_in, n_in, batches):
+def _check_two_calls(ops, lib, plan, w, c_in, n_in, batches, tables):
     wt = plan.pack_weights(torch.from_numpy(w).cuda())
     bias = torch.from_numpy(np.random.RandomState(9).standard_normal(plan.c_out).astype(np.float32)).cuda()
     for call, B in enumerate(batches):
@@ -45,6 +46,12 @@ def _check_two_calls(ops, lib, plan, w, c_in, n_in, batches):
         plan.check()
         # same kernels on the same packed values: identical bits (tolerance of the other tests: 1e-2 rel-L2)
         assert torch.equal(got, want), (call, float((got - want).abs().max()))
+        # ... and the oracle on the same bf16-rounded operands (first rows; the tensor-core tests' bar)
+        r = min(B, 2)
+        xr = x[:r].to(torch.bfloat16).float().cpu().numpy()
+        wr = torch.from_numpy(w).to(torch.bfloat16).float().numpy()
+        ref = oracle.knnconv_forward_closed_form(xr, tables[0], tables[1].astype(np.int64), plan.V, wr, bias.cpu().numpy(), relu=True)
+        assert np.abs(got[:r].permute(0, 2, 1).cpu().numpy() - ref).max() < 2e-3 * max(1.0, np.abs(ref).max())
 
 
 def test_static_scratch_matches_regular_entry_points(golden):
@@ -55,12 +62,12 @@ def test_static_scratch_matches_regular_entry_points(golden):
     g = golden("config1.npz")
     V, n_in = int(g["V"]), int(g["n_in"])
     plan = ops.KnnConvPlan(g["knn_idx_pad"], g["tap"], n_in, V, 3, 64, group=1)   # the C entry point under test takes the plain plan
-    _check_two_calls(ops, lib, plan, kaiming_weight(np.random.RandomState(1), 64, 3, V), 3, n_in, (5, 130))
+    _check_two_calls(ops, lib, plan, kaiming_weight(np.random.RandomState(1), 64, 3, V), 3, n_in, (5, 130), (g["knn_idx_pad"], g["tap"]))
     # channels-last layout (c_in = 64)
     t = golden("config3_tables.npz")
     V = int(t["l1_V"])
     plan = ops.KnnConvPlan(t["l1_knn_idx_pad"], t["l1_tap"], 1023, V, 64, 192)
-    _check_two_calls(ops, lib, plan, kaiming_weight(np.random.RandomState(2), 192, 64, V), 64, 1023, (3, 2))
+    _check_two_calls(ops, lib, plan, kaiming_weight(np.random.RandomState(2), 192, 64, V), 64, 1023, (3, 2), (t["l1_knn_idx_pad"], t["l1_tap"]))
 
 
 def test_static_scratch_rejects_oversized_batch(golden):
