@@ -144,6 +144,32 @@ def test_random_small_cases_vs_oracle(ops, B, Cin, Nin, Nout, K, V, Cout):
     assert np.abs(y16 - ref).max() < 1e-2 * max(1.0, np.abs(ref).max())
 
 
+@pytest.mark.parametrize("B,Cin,Nin,Nout,K,V,Cout", [
+    (600, 64, 30, 90, 5, 9, 192),     # three 256-row tiles, the last one ragged; more work items than CTA pairs
+    (520, 64, 30, 11, 5, 9, 64),      # fewer work items than CTA pairs
+    (300, 128, 30, 50, 7, 16, 576),   # three c_out tiles of 192, two channel chunks
+    (1024, 64, 40, 80, 6, 9, 384),    # two c_out tiles, four batch tiles
+    (512, 64, 30, 74, 3, 4, 128),     # exactly two work items per CTA pair of a 148-SM part
+    (512, 32, 30, 60, 3, 4, 128),     # 32 channels: half a 64-channel box
+])
+def test_pair_kernel_larger_batches(ops, B, Cin, Nin, Nout, K, V, Cout):
+    """CTA-pair kernel at several hundred rows: several batch tiles and c_out tiles per output point, ragged last tile,
+    against the closed form of fovi/arch/knn.py:484-557."""
+    rs = np.random.RandomState(B + Cout)
+    x = rs.standard_normal((B, Cin, Nin)).astype(f32)
+    idx = rs.randint(0, Nin + 1, (K, Nout)).astype(np.int32)
+    idx[:, 0] = Nin                                                # a point with no neighbours at all
+    tap = rs.randint(0, V, (Nout, K)).astype(np.uint16)
+    w = (rs.standard_normal((Cout, Cin * V)) / np.sqrt(Cin * K)).astype(f32)
+    b = rs.standard_normal(Cout).astype(f32)
+    plan = ops.KnnConvPlan(idx, tap, Nin, V, Cin, Cout)
+    ref = oracle.knnconv_forward_closed_form(bf16_round(x), idx, tap.astype(np.int64), V, bf16_round(w), b, relu=True)
+    for od, tol in ((torch.float32, 2e-3), (torch.bfloat16, 1e-2)):
+        y = run_tc(ops, plan, x, w, b, relu=True, out_dtype=od)
+        assert np.abs(y - ref).max() < tol * max(1.0, np.abs(ref).max()), (od, np.abs(y - ref).max())
+    np.testing.assert_allclose(run_tc(ops, plan, x, w, b, relu=True)[:, :, 0], np.broadcast_to(np.maximum(b, 0), (B, Cout)), rtol=1e-6, atol=1e-6)
+
+
 def test_linearity_and_determinism_full_batch(ops, golden):
     """Size-independent properties at a full batch tile count: f(x1 + x2) == f(x1) + f(x2) without
     bias, and two runs give the same bits."""
