@@ -348,16 +348,22 @@ def extra_patch_embeddings(torch, dev, flush, hbm_gbs, big):
 
 
 def extra_training_step(torch, dev, stack, n0, rows):
-    """Forward + backward of the config-3 stack at `rows` image x fixations (sum-of-squares loss), in the kernels' layout."""
-    x = torch.rand(rows, 3, n0, device=dev)
+    """Forward + backward of the config-3 stack at `rows` image x fixations in bf16 (as under the reference's autocast
+    training): the stack's output receives a given upstream gradient, every layer computes its weight, bias and input
+    gradients (the first layer: weight and bias)."""
+    x = torch.rand(rows, 3, n0, device=dev).to(torch.bfloat16)
     for p in stack.parameters():
         p.requires_grad_(True)
+    gy = None
 
     def step():
+        nonlocal gy
         for p in stack.parameters():
             p.grad = None
         y = stack(x)
-        (y.float() ** 2).mean().backward()
+        if gy is None:
+            gy = torch.randn(y.shape[0], y.shape[2], y.shape[1], device=dev).to(y.dtype).permute(0, 2, 1)   # y's layout
+        y.backward(gy)
     ts = []
     for i in range(6):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

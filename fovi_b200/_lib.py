@@ -34,6 +34,7 @@ SIGNATURES = {
     "fovi_pack_points": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_forward": (C.c_int, [_P, _P, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knnconv_forward_f32": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, _P]),
+    "fovi_knnconv_forward_scatter_add": (C.c_int, [_P, _P, _P, _P, C.c_int, _P, C.c_int, _P]),
     "fovi_knnconv_selftest_wait_timeout": (C.c_int, [_P, _P, _P, _P, C.c_int, C.c_int, _P]),
     "fovi_knnconv_check": (C.c_int, [_P, _P]),
     "fovi_static_scratch_bytes": (C.c_int64, []),
@@ -45,6 +46,7 @@ SIGNATURES = {
     "fovi_knn_depthwise_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knn_depthwise_backward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),
     "fovi_column_sum": (C.c_int, [_P, C.c_int, C.c_longlong, C.c_int, _P, _P]),
+    "fovi_tap_segment_sum": (C.c_int, [_P, C.c_int, C.c_longlong, _P, _P, C.c_int, _P, C.c_int, _P]),
     "fovi_batch_to_inner": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, _P, C.c_int, C.c_int, _P]),
     "fovi_knn_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_tap_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, _P, _P]),

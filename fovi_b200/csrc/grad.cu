@@ -106,7 +106,45 @@ __global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ s
   }
 }
 
+// Segment sums for the weight gradient of a layer with few input channels.  prod [R][S][4] float32 holds, per output
+// channel o (row) and per slot s = (output point, neighbour), the four channel products of that pair; every slot
+// belongs to one filter tap.  dst[o][v*4 + c] += sum over the slots of tap v (listed in seg_slot[seg_start[v] ..
+// seg_start[v+1])) of prod[o][s][c].  One block per (tap, 64 rows): 4 groups of 64 threads walk the list, each thread
+// keeps the float4 of its row, the groups meet in shared memory.  Every dst element has one owner, so no atomics.
+__global__ void __launch_bounds__(256) tap_segment_sum_kernel(const float4* __restrict__ prod, long long S, const int* __restrict__ seg_start,
+                                                             const int* __restrict__ seg_slot, int R, float* __restrict__ dst, int dst_pitch) {
+  __shared__ float4 part[4][64];
+  const int v = blockIdx.x, o = blockIdx.y * 64 + (threadIdx.x & 63), g = threadIdx.x >> 6;
+  const int p0 = __ldg(seg_start + v), p1 = __ldg(seg_start + v + 1);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (o < R) {
+    const float4* row = prod + (long long)o * S;
+    for (int p = p0 + g; p < p1; p += 4) {
+      const float4 q = __ldg(row + __ldg(seg_slot + p));
+      acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+    }
+  }
+  part[g][threadIdx.x & 63] = acc;
+  __syncthreads();
+  if (g == 0 && o < R) {
+    for (int w = 1; w < 4; ++w) { const float4 q = part[w][threadIdx.x]; acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w; }
+    float* d = dst + (long long)o * dst_pitch + 4 * v;
+    d[0] += acc.x; d[1] += acc.y; d[2] += acc.z; d[3] += acc.w;
+  }
+}
+
 }  // namespace
+
+extern "C" int fovi_tap_segment_sum(const float* prod, int R, long long S, const int* seg_start, const int* seg_slot, int V, float* dst,
+                                    int dst_pitch, void* stream) {
+  if (!prod || !seg_start || !seg_slot || !dst || R <= 0 || S <= 0 || V <= 0 || dst_pitch < 4 * V) return FOVI_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(prod) & 15) return FOVI_ERR_ALIGNMENT;
+  if ((R + 63) / 64 > 65535) return FOVI_ERR_UNSUPPORTED;
+  dim3 grid(V, (R + 63) / 64);
+  tap_segment_sum_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float4*>(prod), S, seg_start, seg_slot, R, dst,
+                                                                                    dst_pitch);
+  return fovi::after_launch("tap_segment_sum_kernel");
+}
 
 extern "C" int fovi_column_sum(const void* src, int dtype, long long R, int C, float* dst, void* stream) {
   if (!fovi::valid_dtype(dtype) || R < 0 || C <= 0 || !dst) return FOVI_ERR_INVALID_ARGUMENT;

@@ -319,7 +319,8 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       tc_fence_after();
       const int row = mt * BM + q * 32 + lane;
       const int o0 = ctile * a.ct;
-      const size_t y_off = ((size_t)row * a.n_out + n) * a.c_out + o0;
+      const int n_y = a.out_map ? __ldg(a.out_map + n) : n;
+      const size_t y_off = ((size_t)row * a.n_out_y + n_y) * a.c_out + o0;
       const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + acc * a.acc_cols;
       // 64 accumulator columns per round: two 32-column tensor-memory loads in flight, one wait
       for (int c0 = 0; c0 < a.ct; c0 += 64) {
@@ -351,7 +352,13 @@ fovi_knnconv_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
               for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
             }
             if (row < a.B) {
-              if (a.y_f32) {
+              if (a.accumulate) {
+                float* dst = reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16;
+                if (cnt > 0) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) red_add_f32x4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+              } else if (a.y_f32) {
                 float* dst = reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16;
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
@@ -428,7 +435,7 @@ int fovi::encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, u
 }
 
 static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype, int B,
-                                int relu, void* stream, int skip_loads, uint32_t wait_limit) {
+                                int relu, void* stream, int skip_loads, uint32_t wait_limit, const OutMode& om = OutMode()) {
   if (!p || B < 0 || !fovi::valid_dtype(y_dtype)) return FOVI_ERR_INVALID_ARGUMENT;
   if (B == 0) return FOVI_OK;  // an empty batch has no buffers to look at
   if (!X || !Wt || !Y) return FOVI_ERR_INVALID_ARGUMENT;
@@ -444,7 +451,7 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   const bool c64 = cp >= FOVI_TC_C64_MIN && p->x_layout != FOVI_X_PAIRS;
   // 64-channel layers with more than one batch tile run on CTA pairs (half the weight traffic per SM).
   if (c64 && !FOVI_TC_SINGLE_CTA_ONLY && B > BM && ct % 32 == 0) {
-    const int rc2 = fovi::launch_knnconv_tc_pair(p, X, Wt, bias, Y, y_dtype, B, relu, reinterpret_cast<cudaStream_t>(stream), skip_loads, wait_limit);
+    const int rc2 = fovi::launch_knnconv_tc_pair(p, X, Wt, bias, Y, y_dtype, B, relu, reinterpret_cast<cudaStream_t>(stream), skip_loads, wait_limit, om);
     if (rc2 != FOVI_ERR_UNSUPPORTED) return rc2;
   }
 
@@ -456,6 +463,7 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt = (B + BM - 1) / BM;
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
   a.wait_limit = wait_limit; a.skip_loads = skip_loads;
+  a.out_map = om.out_map; a.n_out_y = om.out_map ? om.n_out_y : p->n_out; a.accumulate = om.accumulate;
   a.mt_fastest = pairs ? 1 : 0;
   const long long items = (long long)a.n_mt * p->n_out * a.n_ct;
   if (items >= (1ll << 31)) return FOVI_ERR_UNSUPPORTED;
@@ -511,6 +519,14 @@ static int knnconv_forward_impl(fovi_knnconv_plan* p, const void* X, const void*
 extern "C" int fovi_knnconv_forward(fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y,
                                     int y_dtype, int B, int relu, void* stream) {
   return knnconv_forward_impl(p, X, Wt, bias, Y, y_dtype, B, relu, stream, 0, WAIT_LIMIT);
+}
+
+extern "C" int fovi_knnconv_forward_scatter_add(fovi_knnconv_plan* p, const void* X, const void* Wt, float* Y, int B, const int* out_map,
+                                               int n_out_y, void* stream) {
+  if (!out_map || n_out_y <= 0) return FOVI_ERR_INVALID_ARGUMENT;
+  OutMode om;
+  om.out_map = out_map; om.n_out_y = n_out_y; om.accumulate = 1;
+  return knnconv_forward_impl(p, X, Wt, nullptr, Y, FOVI_F32, B, 0, stream, 0, WAIT_LIMIT, om);
 }
 
 extern "C" int fovi_knnconv_selftest_wait_timeout(fovi_knnconv_plan* p, const void* X, const void* Wt, void* Y, int y_dtype, int B,

@@ -25,6 +25,7 @@ struct Tc2Args {
   int ct, n_ct, n_mt2, nstage, relu, y_f32, total_items;
   uint32_t stage_bytes, table_bytes;
   uint32_t wait_limit; int skip_loads;   // as in TcArgs
+  const int* out_map; int n_out_y; int accumulate;   // see OutMode
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -235,7 +236,8 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
       tc_fence_after();
       const int row = (mt2 * 2 + (int)rank) * BM + q * 32 + lane;
       const int o0 = ctile * a.ct;
-      const size_t y_off = ((size_t)row * a.n_out + n) * a.c_out + o0;
+      const int n_y = a.out_map ? __ldg(a.out_map + n) : n;
+      const size_t y_off = ((size_t)row * a.n_out_y + n_y) * a.c_out + o0;
       const uint32_t t_base = tmem + ((uint32_t)(q * 32) << 16) + acc * 256u;
       for (int c0 = 0; c0 < a.ct; c0 += 64) {
         uint32_t r[64];
@@ -265,7 +267,13 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
               for (int i = 0; i < 16; ++i) v[i] = fmaxf(v[i], 0.f);
             }
             if (row < a.B) {
-              if (a.y_f32) {
+              if (a.accumulate) {
+                float* dst = reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16;
+                if (cnt > 0) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) red_add_f32x4(dst + 4 * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+              } else if (a.y_f32) {
                 float* dst = reinterpret_cast<float*>(a.Y) + y_off + c0 + g * 16;
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {
@@ -307,7 +315,7 @@ fovi_knnconv_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gri
 }  // namespace
 
 int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype,
-                                 int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit) {
+                                 int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit, const OutMode& om) {
   const int ct = p->ct, cp = p->cin_packed;
   if (p->x_layout != FOVI_X_BNC || cp < 16 || !ct || ct % 32 || ct < 32 || B <= BM) return FOVI_ERR_UNSUPPORTED;
   const int sms = fovi::sm_count();
@@ -319,6 +327,7 @@ int fovi::launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, cons
   a.ct = ct; a.n_ct = p->c_out / ct; a.n_mt2 = (B + 2 * BM - 1) / (2 * BM);
   a.relu = relu; a.y_f32 = y_dtype == FOVI_F32;
   a.wait_limit = wait_limit; a.skip_loads = skip_loads;
+  a.out_map = om.out_map; a.n_out_y = om.out_map ? om.n_out_y : p->n_out; a.accumulate = om.accumulate;
   const long long items = (long long)a.n_mt2 * p->n_out * a.n_ct;
   if (items >= (1ll << 31) || a.kp > 32 * TBQ) return FOVI_ERR_UNSUPPORTED;
   a.total_items = (int)items;

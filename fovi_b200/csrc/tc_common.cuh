@@ -8,6 +8,14 @@
 
 #include "knnconv_plan.cuh"
 
+namespace fovi {
+// Where an output point's result goes.  Normally point n of the plan is point n of Y.  The weight-gradient contraction
+// (one "output point" per part of a filter tap's pair list) instead ADDS every part into its tap's row of a float32 Y:
+// out_map[n] is the row, n_out_y the number of rows of Y, and the stores become float32 reductions.
+struct OutMode { const int* out_map = nullptr; int n_out_y = 0; int accumulate = 0; };
+}  // namespace fovi
+using fovi::OutMode;
+
 namespace {
 
 constexpr int BM = 128;            // batch rows per tile (UMMA M)
@@ -30,6 +38,7 @@ struct TcArgs {
   uint32_t acc_cols, tmem_cols;  // columns per accumulator (power of two >= ct) and allocated in total (two accumulators)
   const unsigned char* X; const unsigned char* Wt; const unsigned char* zero_block; int n_pairs;  // PAIRS mode
   uint32_t stage_bytes, table_bytes;
+  const int* out_map; int n_out_y; int accumulate;   // see OutMode
 };
 
 // ---------------------------------------------------------------- PTX wrappers
@@ -118,6 +127,11 @@ __device__ __forceinline__ void st_global_32(void* p, const uint32_t (&w)[8]) {
   }
 }
 
+// Four float32 reductions in one instruction (16-byte aligned).
+__device__ __forceinline__ void red_add_f32x4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // Shared-memory matrix descriptor (K-major operand).  layout: 0 = no swizzle, 2 = 128-byte swizzle.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
   uint64_t d = 0;
@@ -184,5 +198,5 @@ int encode_3d(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_
               uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128);
 // CTA-pair variant of the 64-channel mode (knnconv_tc2.cu).  Returns FOVI_ERR_UNSUPPORTED when it does not apply.
 int launch_knnconv_tc_pair(const fovi_knnconv_plan* p, const void* X, const void* Wt, const float* bias, void* Y, int y_dtype,
-                           int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit);
+                           int B, int relu, cudaStream_t st, int skip_loads, uint32_t wait_limit, const OutMode& om);
 }  // namespace fovi

@@ -12,7 +12,7 @@ themselves table-driven gather-GEMMs, so each runs as a forward launch of ``fovi
   points m holding ``X^T [m][c][b]`` in the packed-weight layout, and there is one "output point" per filter tap v whose
   neighbour list is every (n, m) pair that uses v
   (``dW[o,c,v] = sum_{(n,k): tap[n,k]=v} sum_b dY[b,n,o] * X[b,idx[k,n],c]``).  Lists longer than the kernel's limit are
-  split and the parts summed.  Layers with at most 4 input channels use one GEMM per output point instead (see
+  split and the parts added into their tap's rows by the kernel's epilogue.  Layers with at most 4 input channels use one GEMM per output point instead (see
   ``_weight_grad_few``).
 
 Operands are bf16 with float32 accumulation, as under the reference's autocast training.
@@ -56,7 +56,7 @@ class KnnConvGrad:
         self.n_in, self.V, self.c_in, self.c_out, self.device = int(n_in), int(V), int(c_in), int(c_out), device
         self.K, self.n_out = idx.shape
         ks, ns = np.nonzero(idx != n_in)
-        self._n, self._m, self._v = ns, idx[ks, ns], tp[ns, ks]
+        self._n, self._m, self._v, self._k = ns, idx[ks, ns], tp[ns, ks], ks
         self._idx, self._tap, self._few = idx, tp, None
         self._dx_plan = None
         self._dw_plans = {}
@@ -100,25 +100,33 @@ class KnnConvGrad:
             plan = ops.KnnConvPlan(idx_w, tap_w, self.n_out, self.n_in, bp, self.c_in_pad, device=self.device)
             if not plan.tc_supported:
                 raise NotImplementedError("the weight-gradient contraction is outside the tensor-core kernel's shapes")
-            self._dw_plans[bp] = (plan, parts if isinstance(parts, int) else torch.from_numpy(parts).to(self.device))
+            owner = np.arange(n_groups) // parts if isinstance(parts, int) else parts          # tap of each part
+            self._dw_plans[bp] = (plan, torch.from_numpy(np.ascontiguousarray(owner, dtype=np.int32)).to(self.device))
         return self._dw_plans[bp]
 
     # ---- dW of a layer with at most 4 input channels
     # One tap's pair list would give MMAs of only c_in columns (a 64x3 outer product per pair fills 9 % of an MMA).  Instead
     # there is one GEMM per output point n: rows = output channels, columns = (neighbour k, channel c), contraction over the
     # batch, P_n[o,(k,c)] = sum_b dY[b,n,o] * X[b,idx[k,n],c].  To the kernel this is a layer in which point n has the single
-    # neighbour n and its own "weight slab": X^T gathered by n's neighbour list, [n][(k,c)][b].  The products are then
-    # added into dW[o,c,tap[n,k]].  Points are processed in chunks so that the gathered operand stays near 256 MB.
+    # neighbour n and its own "weight slab": X^T gathered by n's neighbour list, [n][(k,c)][b].  The products of every
+    # filter tap's pairs are then summed into dW[o,c,tap] by a segment-sum kernel (fovi_tap_segment_sum).  Points are processed in chunks so that the gathered operand stays near 256 MB.
     def _few_tables(self, idx, tap):
         K, kp = self.K, (-(-self.K // 4) * 4 if self.K <= 64 else -(-self.K // 64) * 64)
         gather = np.full((self.n_out, kp), self.n_in, np.int64)          # row n_in of the operand is zero
         gather[:, :K] = idx.T
-        target = np.full((self.n_out, kp, 4), self.V * 4, np.int64)      # column V*4 of the accumulator is a dump
-        valid = (idx.T != self.n_in)
-        t4 = tap[:, :, None] * 4 + np.arange(4)[None, None, :]
-        t4 = np.where(valid[:, :, None] & (np.arange(4)[None, None, :] < self.c_in), t4, self.V * 4)
-        target[:, :K] = t4
-        return kp, torch.from_numpy(gather).to(self.device), torch.from_numpy(target).to(self.device)
+        return kp, torch.from_numpy(gather).to(self.device)
+
+    def _few_segments(self, n0, npts, kp):
+        """Slots (n - n0) * kp + k of the chunk's valid (output point, neighbour) pairs, grouped by filter tap."""
+        key = ("seg", n0, npts)
+        if key not in self._dw_plans:
+            sel = (self._n >= n0) & (self._n < n0 + npts)
+            n, v, ks = self._n[sel], self._v[sel], self._k[sel]
+            order = np.argsort(v, kind="stable")
+            start = np.searchsorted(v[order], np.arange(self.V + 1)).astype(np.int32)
+            slot = ((n[order] - n0) * kp + ks[order]).astype(np.int32)
+            self._dw_plans[key] = (torch.from_numpy(start).to(self.device), torch.from_numpy(slot).to(self.device))
+        return self._dw_plans[key]
 
     def _few_plan(self, bp, n0, npts):
         key = ("few", bp, n0, npts)
@@ -136,18 +144,19 @@ class KnnConvGrad:
         bp = -(-B // 64) * 64
         if self._few is None:
             self._few = self._few_tables(self._idx, self._tap)
-        kp, gather, target = self._few
+        kp, gather = self._few
         gy_t = ops.batch_to_inner(gy, bp=bp)                                            # [c_out, n_out, bp]
         x_t = torch.zeros((self.n_in + 1, 4, bp), dtype=torch.bfloat16, device=x.device)
         ops.batch_to_inner(x.permute(0, 2, 1), jp=4, bp=bp, out=x_t[:self.n_in])        # [n_in (+ zero row), 4, bp]
-        dw = torch.zeros((self.c_out, self.V * 4 + 1), dtype=torch.float32, device=gy.device)
+        dw = torch.zeros((self.c_out, self.V * 4), dtype=torch.float32, device=gy.device)
         chunk = max(1, min(self.n_out, 0xFFFF, (256 << 20) // (kp * 4 * bp * 2)))
         for n0 in range(0, self.n_out, chunk):
             npts = min(chunk, self.n_out - n0)
             slab = x_t[gather[n0:n0 + npts]].reshape(npts, kp * 4, bp)                  # [n][(k,c)][b]
             prod = self._few_plan(bp, n0, npts).forward(gy_t, slab, out_dtype=torch.float32)    # [c_out, npts, kp*4]
-            dw.index_add_(1, target[n0:n0 + npts].reshape(-1), prod.reshape(self.c_out, -1))
-        return dw[:, :self.V * 4].reshape(self.c_out, self.V, 4)[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)
+            seg_start, seg_slot = self._few_segments(n0, npts, kp)
+            ops.tap_segment_sum(prod.view(self.c_out, npts * kp, 4), seg_start, seg_slot, dw)   # every tap sums its pairs
+        return dw.reshape(self.c_out, self.V, 4)[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)
 
     def weight_grad(self, gy, x):
         """gy [B, c_out, n_out] and x [B, c_in, n_in] (any strides/dtype) -> dW [c_out, c_in*V] float32."""
@@ -155,15 +164,12 @@ class KnnConvGrad:
             return self._weight_grad_few(gy, x)
         B = gy.shape[0]
         bp = -(-B // 64) * 64
-        plan, parts_per_tap = self.dw_plan(bp)
+        plan, owner = self.dw_plan(bp)
         gy_t = ops.batch_to_inner(gy, bp=bp)                                           # [c_out, n_out, bp]
         x_t = ops.batch_to_inner(x.permute(0, 2, 1), jp=self.c_in_pad, bp=bp)          # [n_in, c_in_pad, bp]
-        parts = plan.forward(gy_t, x_t, out_dtype=torch.float32)                # [c_out, V * parts_per_tap, c_in_pad]
-        if isinstance(parts_per_tap, int):
-            dw = parts.view(self.c_out, self.V, parts_per_tap, self.c_in_pad).sum(2) if parts_per_tap > 1 else parts
-        else:
-            dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
-            dw.index_add_(1, parts_per_tap, parts)
+        # every part of a tap's list is reduced into the tap's rows by the kernel's epilogue (float32 reductions in L2)
+        dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
+        plan.forward_scatter_add(gy_t, x_t, owner, dw)
         return dw[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)
 
 

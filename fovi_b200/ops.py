@@ -267,6 +267,20 @@ class KnnConvPlan:
                                            _dt(out.dtype), B, int(relu), _stream()), "fovi_knnconv_forward")
         return out
 
+    def forward_scatter_add(self, x_bnc, wt, out_map, out):
+        """Tensor-core path whose output point n is ADDED into out[:, out_map[n], :] (out: float32 [B, n_out_y, c_out],
+        initialised by the caller; out_map: int32 [n_out] on the device).  See fovi_knnconv_forward_scatter_add."""
+        _need_cuda(x_bnc, wt, out_map, out)
+        assert self.x_layout != X_PAIRS and x_bnc.dtype == torch.bfloat16 and x_bnc.is_contiguous() and wt.dtype == torch.bfloat16 and wt.is_contiguous()
+        B = x_bnc.shape[0]
+        assert x_bnc.shape[1:] == (self.n_in, self.cin_packed) and wt.shape == (self.V, self.c_out, self.cin_packed)
+        assert out_map.dtype == torch.int32 and out_map.is_contiguous() and out_map.numel() == self.n_out
+        assert out.dtype == torch.float32 and out.is_contiguous() and out.dim() == 3 and out.shape[0] == B and out.shape[2] == self.c_out
+        with torch.cuda.device(x_bnc.device):
+            check(lib.fovi_knnconv_forward_scatter_add(self._h_tc, _ptr(x_bnc), _ptr(wt), _ptr(out), B, _ptr(out_map), int(out.shape[1]),
+                                                       _stream()), "fovi_knnconv_forward_scatter_add")
+        return out
+
     def forward_f32(self, x, wt_f32, bias=None, relu=False, x_layout=ACT_BCN, y_layout=ACT_BCN):
         """Exact float32 path.  x [B,c_in,n_in] (BCN) or [B,n_in,c_in] (BNC)."""
         _need_cuda(x, wt_f32, bias)
@@ -469,6 +483,19 @@ def column_sum(x):
     with torch.cuda.device(x.device):
         check(lib.fovi_column_sum(_ptr(x), _dt(x.dtype), x.numel() // Cc, Cc, _ptr(out), _stream()), "fovi_column_sum")
     return out
+
+
+def tap_segment_sum(prod, seg_start, seg_slot, dst):
+    """dst[o, 4*v + c] += sum over the slots of tap v of prod[o, slot, c]  (prod float32 [R, S, 4] contiguous, seg_start int32 [V+1],
+    seg_slot int32, dst float32 [R, >= 4*V] contiguous).  See fovi_tap_segment_sum."""
+    _need_cuda(prod, seg_start, seg_slot, dst)
+    assert prod.dtype == torch.float32 and prod.is_contiguous() and prod.dim() == 3 and prod.shape[2] == 4
+    assert seg_start.dtype == torch.int32 and seg_slot.dtype == torch.int32 and dst.dtype == torch.float32 and dst.is_contiguous()
+    V = seg_start.numel() - 1
+    with torch.cuda.device(prod.device):
+        check(lib.fovi_tap_segment_sum(_ptr(prod), prod.shape[0], prod.shape[1], _ptr(seg_start), _ptr(seg_slot), V, _ptr(dst), dst.shape[1],
+                                       _stream()), "fovi_tap_segment_sum")
+    return dst
 
 
 def launch_count():

@@ -216,6 +216,15 @@ int fovi_knnconv_forward_f32(const fovi_knnconv_plan* plan, const void* X, int x
                              const float* Wt, const float* bias, float* Y, int y_layout, int B, int relu,
                              void* stream);
 
+/* Tensor-core forward whose results are ADDED into rows of a float32 Y instead of stored: output point n of the plan adds
+ * its [B, c_out] block into Y[:, out_map[n], :] (Y: [B, n_out_y, c_out] float32, initialised by the caller; out_map: device
+ * int32 [n_out] with values in [0, n_out_y); no bias, no ReLU).  The additions are float32 reductions in L2, so their order --
+ * and with it the last bits of Y -- may differ between runs.  This is the weight-gradient contraction of KNNConv
+ * (fovi/arch/knn.py:538-557 under autograd): one "output point" per part of a filter tap's (output point, neighbour) list,
+ * every part reduced into its tap (fovi_b200/grad.py), where the reference's autograd uses index_add-style scatter kernels. */
+int fovi_knnconv_forward_scatter_add(fovi_knnconv_plan* plan, const void* X, const void* Wt, float* Y, int B, const int* out_map,
+                                     int n_out_y, void* stream);
+
 /* Diagnostic for the failure path: launches the plan's tensor-core kernel with every operand load withheld and a short
  * wait limit, so the kernel's first consumer waits run out.  Nothing faults or hangs: the kernel records the wait site,
  * all its roles leave, tensor memory is freed.  A following fovi_knnconv_check must return FOVI_ERR_DEVICE_TIMEOUT, and
@@ -275,6 +284,13 @@ int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long lo
 /* Bias gradient: dst[c] = sum over the R rows of the row-major [R, C] matrix src (bf16 or float32, C even), float32
  * accumulation; dst is overwritten.  (The reference: autograd of the bias add in F.linear, fovi/arch/knn.py:555.) */
 int fovi_column_sum(const void* src, int dtype, long long R, int C, float* dst, void* stream);
+
+/* Segment sums of the weight gradient of a layer with at most 4 input channels (fovi_b200/grad.py): prod is float32
+ * [R][S][4] (row = output channel, slot = (output point, neighbour) pair, 4 channel products); the slots of filter tap v are
+ * seg_slot[seg_start[v] .. seg_start[v+1]) (device int32 arrays, seg_start has V+1 entries).
+ * dst[o*dst_pitch + 4*v + c] += sum of prod[o][slot][c] over the tap's slots.  No atomics: results are deterministic. */
+int fovi_tap_segment_sum(const float* prod, int R, long long S, const int* seg_start, const int* seg_slot, int V, float* dst,
+                         int dst_pitch, void* stream);
 
 
 /* ------------------------------------------------------------------------------------------

@@ -170,6 +170,33 @@ def test_pair_kernel_larger_batches(ops, B, Cin, Nin, Nout, K, V, Cout):
     np.testing.assert_allclose(run_tc(ops, plan, x, w, b, relu=True)[:, :, 0], np.broadcast_to(np.maximum(b, 0), (B, Cout)), rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("B,Cin,Nin,Nout,K,V,Cout", [
+    (40, 64, 30, 23, 5, 9, 64),       # one batch tile: single-CTA kernel
+    (300, 128, 30, 23, 7, 16, 192),   # CTA pairs, ragged second pair tile
+])
+def test_scatter_add_output(ops, B, Cin, Nin, Nout, K, V, Cout):
+    """fovi_knnconv_forward_scatter_add: output point n is added into row out_map[n] of a float32 result that already
+    holds values; checked against the closed form summed the same way."""
+    rs = np.random.RandomState(B)
+    x = rs.standard_normal((B, Cin, Nin)).astype(f32)
+    idx = rs.randint(0, Nin + 1, (K, Nout)).astype(np.int32)
+    idx[:, 0] = Nin
+    tap = rs.randint(0, V, (Nout, K)).astype(np.uint16)
+    w = (rs.standard_normal((Cout, Cin * V)) / np.sqrt(Cin * K)).astype(f32)
+    rows = 5
+    out_map = rs.randint(0, rows, Nout).astype(np.int32)
+    init = rs.standard_normal((B, rows, Cout)).astype(f32)
+    plan = ops.KnnConvPlan(idx, tap, Nin, V, Cin, Cout)
+    ref = oracle.knnconv_forward_closed_form(bf16_round(x), idx, tap.astype(np.int64), V, bf16_round(w), None)   # [B, Cout, Nout]
+    want = init.copy()
+    np.add.at(want, (slice(None), out_map), ref.transpose(0, 2, 1))
+    out = dev(init.copy())
+    plan.forward_scatter_add(ops.pack_points(dev(x), plan), plan.pack_weights(dev(w)), dev(out_map), out)
+    plan.check()
+    got = out.cpu().numpy()
+    assert np.abs(got - want).max() < 2e-3 * max(1.0, np.abs(want).max()), np.abs(got - want).max()
+
+
 def test_linearity_and_determinism_full_batch(ops, golden):
     """Size-independent properties at a full batch tile count: f(x1 + x2) == f(x1) + f(x2) without
     bias, and two runs give the same bits."""
