@@ -45,6 +45,9 @@ SIGNATURES = {
     "fovi_knnconv_pack_weights_grouped": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_knn_depthwise_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, _P, C.c_int, C.c_int, C.c_int, C.c_int, _P]),
     "fovi_knn_depthwise_backward": (C.c_int, [_P, _P, C.c_int, C.c_int, _P, _P, C.c_int, C.c_int, C.c_int, _P, _P, _P]),
+    "fovi_sensor_ring_layout": (C.c_longlong, [C.c_double, C.c_double, C.c_int, _P, _P]),
+    "fovi_sensor_points": (C.c_int, [C.c_double, C.c_double, C.c_int, C.c_double, C.c_longlong, _P, _P, _P]),
+    "fovi_sensor_pad_points": (C.c_longlong, [C.c_double, C.c_double, C.c_int, C.c_double, C.c_double, C.c_longlong, _P, _P]),
     "fovi_column_sum": (C.c_int, [_P, C.c_int, C.c_longlong, C.c_int, _P, _P]),
     "fovi_tap_segment_sum": (C.c_int, [_P, C.c_int, C.c_longlong, _P, _P, C.c_int, _P, C.c_int, _P]),
     "fovi_batch_to_inner": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, _P, C.c_int, C.c_int, _P]),

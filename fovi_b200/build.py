@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(CSRC, "build")
 LIB = os.path.join(HERE, "libfovi_b200.so")
-SOURCES = ["capi.cu", "sampler.cu", "knnconv.cu", "knnconv_tc.cu", "knnconv_tc2.cu", "knnpool.cu", "knnnorm.cu", "fused.cu", "tables.cu", "grad.cu", "depthwise.cu"]
+SOURCES = ["capi.cu", "sampler.cu", "knnconv.cu", "knnconv_tc.cu", "knnconv_tc2.cu", "knnpool.cu", "knnnorm.cu", "fused.cu", "tables.cu", "geometry.cu", "grad.cu", "depthwise.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 

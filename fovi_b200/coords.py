@@ -16,7 +16,9 @@ arc spacing equal to the local ring spacing (isotropy).  A point at eccentricity
 angle theta sits on the 3-D cortical manifold at ``(rho cos theta, rho sin theta, z)`` with
 ``rho = M(r) sin(r) 180/pi``, ``M(r) = k/(a + r)`` and ``z = integral sqrt(M^2 - rho'^2) dr``.
 """
+import ctypes as C
 import math
+import os
 
 import numpy as np
 import torch
@@ -30,11 +32,48 @@ _MANIFOLD_K = 10.0          # mm scale of the magnification function (fovi/sensi
 _MESH_STEP = 0.0001         # degrees, integration mesh of the manifold's z (manifold.py:44-48)
 
 
-def ring_layout(fov, cmf_a, res):
+def default_builder():
+    """'torch' (default): the reference's own library calls, bit-identical coordinates on the machine that recorded
+    the fixtures.  'native': the library's host routines (``fovi_sensor_ring_layout`` / ``fovi_sensor_points`` /
+    ``fovi_sensor_pad_points``): the same point counts, coordinates within a few float32 ulps, no torch / SciPy call
+    and 10-100x faster ring-count searches.  Set with the environment variable ``FOVI_B200_GEOMETRY``."""
+    b = os.environ.get("FOVI_B200_GEOMETRY", "torch")
+    if b not in ("torch", "native"):
+        raise ValueError("FOVI_B200_GEOMETRY must be 'torch' or 'native'")
+    return b
+
+
+def _native_ring_layout(fov, cmf_a, res):
+    from ._lib import lib
+    radius, counts = np.empty(res, np.float32), np.empty(res, np.int32)
+    n = lib.fovi_sensor_ring_layout(float(fov), float(cmf_a), int(res), radius.ctypes.data_as(C.c_void_p), counts.ctypes.data_as(C.c_void_p))
+    if n < 0:
+        raise ValueError(f"fovi_sensor_ring_layout({fov}, {cmf_a}, {res}) failed with code {n}")
+    return torch.from_numpy(radius), [int(c) for c in counts]
+
+
+def _native_points(fov, cmf_a, res, max_val):
+    """(cartesian [N,2], polar [N,2], cortical [N,3]) float64 tensors, (cartesian_pad [P,2], cortical_pad [P,3]) float32."""
+    from ._lib import check, lib
+    ptr = lambda a: a.ctypes.data_as(C.c_void_p)  # noqa: E731
+    n = lib.fovi_sensor_ring_layout(float(fov), float(cmf_a), int(res), None, None)
+    cart, polar, cort = np.empty((n, 2)), np.empty((n, 2)), np.empty((n, 3))
+    check(lib.fovi_sensor_points(float(fov), float(cmf_a), int(res), float(max_val), n, ptr(cart), ptr(polar), ptr(cort)), "fovi_sensor_points")
+    n_pad = lib.fovi_sensor_pad_points(float(fov), float(cmf_a), int(res), float(max_val), 0.5, 0, None, None)
+    if n_pad < 0:
+        raise ValueError(f"fovi_sensor_pad_points failed with code {n_pad}")
+    cart_pad, cort_pad = np.empty((n_pad, 2), np.float32), np.empty((n_pad, 3), np.float32)
+    lib.fovi_sensor_pad_points(float(fov), float(cmf_a), int(res), float(max_val), 0.5, n_pad, ptr(cart_pad), ptr(cort_pad))
+    return [torch.from_numpy(a) for a in (cart, polar, cort, cart_pad, cort_pad)]
+
+
+def ring_layout(fov, cmf_a, res, builder=None):
     """Ring radii (float32 tensor [res], normalised so that fov/2 -> 1) and angles per ring (list of int).
     Follows fovi/sensing/coords.py:322-370: float32 ``linspace``/``exp``; a ring's angle count is the
     length of ``arange(0, 2*pi*r, mean ring spacing)``, i.e. ``ceil`` of the ratio taken in double."""
     res = int(res)
+    if (builder or default_builder()) == "native":
+        return _native_ring_layout(fov, cmf_a, res)
     w_lo, w_hi = np.log(cmf_a), np.log(fov / 2 + cmf_a)
     dw = (w_hi - w_lo) / (res - 1)
     r = torch.exp(torch.linspace(w_lo, w_hi + dw, steps=res + 1)) - cmf_a      # one extra ring for the last spacing
@@ -140,16 +179,22 @@ class SamplingCoords:
     field of view ``cartesian_pad_coords`` / ``cortical_pad_coords``, and ``shape``.
     """
 
-    def __init__(self, fov, cmf_a, res, device="cpu", style="isotropic", dtype=torch.float, max_val=1):
+    def __init__(self, fov, cmf_a, res, device="cpu", style="isotropic", dtype=torch.float, max_val=1, builder=None):
         _check_style(style)
         self.fov, self.cmf_a, self.resolution = fov, cmf_a, res
         self.device, self.style, self.dtype, self.max_val = device, style, dtype, max_val
+        self.builder = builder or default_builder()
         self.plotting = None      # the reference's plotting coordinates are not part of the hot path
         if res == 1:
             z2, z3 = torch.zeros(1, 2, dtype=dtype), torch.zeros(1, 3, dtype=dtype)
             self.cartesian, self.polar, self.cortical = z2, z2.clone(), z3
+        elif self.builder == "native":
+            cart64, polar64, cort64, cart_pad, cort_pad = _native_points(fov, cmf_a, res, float(max_val))
+            self.cartesian_rowcol = torch.stack([-cart64[:, 1], cart64[:, 0]], 1)
+            self.cartesian_pad_coords, self.cortical_pad_coords = cart_pad.to(dtype), cort_pad.to(dtype)
+            self.cartesian, self.polar, self.cortical = cart64, polar64, cort64
         else:
-            radius, counts = ring_layout(fov, cmf_a, res)
+            radius, counts = ring_layout(fov, cmf_a, res, builder="torch")
             radius = radius * max_val
             ring = torch.repeat_interleave(radius.double(), torch.tensor(counts))
             angle = torch.from_numpy(np.concatenate([np.linspace(0, 2 * np.pi, n, endpoint=False) for n in counts]))
@@ -191,7 +236,7 @@ class SamplingCoords:
             rings = self.resolution // stride
         if rings < 1:
             raise ValueError(f"stride {stride} leaves fewer than one ring ({rings})")
-        return SamplingCoords(self.fov, self.cmf_a, rings, self.device, self.style, self.dtype, max_val=max_val), rings, out_cart_res
+        return SamplingCoords(self.fov, self.cmf_a, rings, self.device, self.style, self.dtype, max_val=max_val, builder=self.builder), rings, out_cart_res
 
     def to(self, device=None, dtype=None):
         self.dtype = self.dtype if dtype is None else dtype
@@ -202,7 +247,8 @@ class SamplingCoords:
         return self
 
     def clone(self, **overrides):
-        args = dict(fov=self.fov, cmf_a=self.cmf_a, res=self.resolution, device=self.device, style=self.style, dtype=self.dtype, max_val=self.max_val)
+        args = dict(fov=self.fov, cmf_a=self.cmf_a, res=self.resolution, device=self.device, style=self.style, dtype=self.dtype, max_val=self.max_val,
+                    builder=self.builder)
         if "resolution" in overrides:
             overrides["res"] = overrides.pop("resolution")
         args.update({k: v for k, v in overrides.items() if v is not None})

@@ -87,17 +87,27 @@ class KnnConvGrad:
         return plan.forward(gy_points, plan.pack_weights(w_t.contiguous()), out_dtype=torch.bfloat16)
 
     # ---- dW
+    @property
+    def dw_swapped(self):
+        """Which operand gives the rows of the weight-gradient GEMM.  An MMA costs about the same whatever its width, so
+        a layer with few input channels and many output channels (64 -> 192) is cheaper the other way round: rows = input
+        channels (one 128-row tile on one SM instead of a 256-row tile on a CTA pair), columns = output channels."""
+        return self.c_in_pad <= 128 < self.c_out
+
     def dw_plan(self, bp):
         if bp not in self._dw_plans:
             # Lists are cut so that there are a few hundred of them (several per SM pair), whatever the number of taps.
             limit = int(min(MAX_LIST, max(8, -(-self._v.size // 300 // 8) * 8)))
             order, gid, pos, n_groups, parts = _grouped(self._v, self.V, limit)
             kw = max(8, int(pos.max()) + 1 if pos.size else 8)
-            idx_w = np.full((kw, n_groups), self.n_out, np.int32)
+            # gathered side ("points") and streamed side ("taps") of a pair: (n, m), or (m, n) when swapped
+            pts, taps = (self._m, self._n) if self.dw_swapped else (self._n, self._m)
+            n_pts, n_taps = (self.n_in, self.n_out) if self.dw_swapped else (self.n_out, self.n_in)
+            idx_w = np.full((kw, n_groups), n_pts, np.int32)
             tap_w = np.zeros((n_groups, kw), np.uint16)
-            idx_w[pos, gid] = self._n[order]
-            tap_w[gid, pos] = self._m[order]
-            plan = ops.KnnConvPlan(idx_w, tap_w, self.n_out, self.n_in, bp, self.c_in_pad, device=self.device)
+            idx_w[pos, gid] = pts[order]
+            tap_w[gid, pos] = taps[order]
+            plan = ops.KnnConvPlan(idx_w, tap_w, n_pts, n_taps, bp, self.c_out if self.dw_swapped else self.c_in_pad, device=self.device)
             if not plan.tc_supported:
                 raise NotImplementedError("the weight-gradient contraction is outside the tensor-core kernel's shapes")
             owner = np.arange(n_groups) // parts if isinstance(parts, int) else parts          # tap of each part
@@ -165,9 +175,15 @@ class KnnConvGrad:
         B = gy.shape[0]
         bp = -(-B // 64) * 64
         plan, owner = self.dw_plan(bp)
-        gy_t = ops.batch_to_inner(gy, bp=bp)                                           # [c_out, n_out, bp]
-        x_t = ops.batch_to_inner(x.permute(0, 2, 1), jp=self.c_in_pad, bp=bp)          # [n_in, c_in_pad, bp]
         # every part of a tap's list is reduced into the tap's rows by the kernel's epilogue (float32 reductions in L2)
+        if self.dw_swapped:
+            x_r = ops.batch_to_inner(x, bp=bp)                                          # rows: [c_in, n_in, bp]
+            gy_w = ops.batch_to_inner(gy.permute(0, 2, 1), jp=self.c_out, bp=bp)        # "weights": [n_out, c_out, bp]
+            dw_t = torch.zeros((self.c_in, self.V, self.c_out), dtype=torch.float32, device=gy.device)
+            plan.forward_scatter_add(x_r, gy_w, owner, dw_t)
+            return dw_t.permute(2, 0, 1).reshape(self.c_out, self.c_in * self.V)
+        gy_t = ops.batch_to_inner(gy, bp=bp)                                           # rows: [c_out, n_out, bp]
+        x_t = ops.batch_to_inner(x.permute(0, 2, 1), jp=self.c_in_pad, bp=bp)          # "weights": [n_in, c_in_pad, bp]
         dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
         plan.forward_scatter_add(gy_t, x_t, owner, dw)
         return dw[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)

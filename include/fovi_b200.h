@@ -302,6 +302,25 @@ int fovi_tap_segment_sum(const float* prod, int R, long long S, const int* seg_s
  * index, so the tables are a function of the coordinates alone.  All pointers are HOST memory; no device is needed.
  * ------------------------------------------------------------------------------------------ */
 
+/* ---- Sensor geometry on the host (no device needed): fovi/sensing/coords.py:204-370 (ring radii evenly spaced in
+ * log(r + a), angles per ring for isotropic spacing), :68-87 (pad rings outside the field of view) and
+ * fovi/sensing/manifold.py:32-48, 139-170 (cortical manifold: rho = M(r) sin(r) 180/pi, z = integral of sqrt(M^2 - rho'^2)).
+ * Same formulas and rounding points as the reference (float32 ring radii, double elsewhere) on the C library's functions:
+ * identical point counts, coordinates within a few units in the last float32 place of the reference's (3e-7 for the
+ * normalised cartesian coordinates, 4e-6 for the cortical ones on the recorded sensors). */
+/* Normalised ring radii (float32 [res], fov/2 -> 1) and angles per ring (int [res]); either may be NULL.
+ * Returns the total number of sample points, or minus a FOVI_ERR_* code. */
+long long fovi_sensor_ring_layout(double fov, double cmf_a, int res, float* radius, int* counts);
+/* The n_points (= fovi_sensor_ring_layout's result) sample points, ring by ring: cartesian [n,2] (x, y in [-max_val, max_val]),
+ * polar [n,2] (radius, angle), cortical [n,3], all double. */
+int fovi_sensor_points(double fov, double cmf_a, int res, double max_val, long long n_points, double* cartesian, double* polar,
+                       double* cortical);
+/* Pad rings continuing outward at the last ring spacing for `padding_distance` (0.5 in the reference), sampled at the same
+ * spacing in angle: cartesian [n,2] and cortical [n,3], float32, `capacity` points of room.  Returns the number of pad points
+ * (with both outputs NULL: only that), or minus a FOVI_ERR_* code. */
+long long fovi_sensor_pad_points(double fov, double cmf_a, int res, double max_val, double padding_distance, long long capacity,
+                                 float* cartesian_pad, float* cortical_pad);
+
 /* pts [n_pts,dim]: the layer's input points followed by its pad ring (cortical or visual-field coordinates);
  * targets [n_out,dim]: the output points.  idx_out [K,n_out]: the K nearest points of each target, nearest first
  * (order: distance, then index); dist_out [K,n_out] (may be NULL): their distances. */

@@ -28,6 +28,41 @@ def test_sensor_coordinates_bit_exact(golden, tag, a):
     assert np.array_equal(grid, g["sampling_grid"])
 
 
+@pytest.mark.parametrize("tag,a", [("a0p5", 0.5), ("a1", 1.0), ("a2p78", 2.78), ("a2p785765", 2.785765), ("a60p94", 60.94)])
+def test_native_sensor_geometry_matches_recorded_sensors(golden, tag, a):
+    """builder='native' (the library's host routines for fovi/sensing/coords.py:204-370, manifold.py:32-48): the same ring
+    count and point counts as the reference's recorded sensors, coordinates within a few float32 ulps, same result twice."""
+    g = golden(f"sensor_{tag}.npz")
+    from fovi_b200 import coords
+    res, n = None, None
+    os.environ["FOVI_B200_GEOMETRY"] = "native"
+    try:
+        assert coords.default_builder() == "native"
+        res, n = find_desired_res(16, a, 64 ** 2, "isotropic", force_less_than=True)
+        c = SamplingCoords(16, a, res)
+    finally:
+        del os.environ["FOVI_B200_GEOMETRY"]
+    assert c.builder == "native" and res == int(g["resolution"]) and n == g["cartesian"].shape[0]
+    for key, attr, tol in (("cartesian", "cartesian", 3e-7), ("polar", "polar", 3e-7), ("cortical", "cortical", 4e-6),
+                           ("cartesian_pad", "cartesian_pad_coords", 5e-7), ("cortical_pad", "cortical_pad_coords", 6e-6)):
+        got = getattr(c, attr).numpy()
+        assert got.shape == g[key].shape and got.dtype == g[key].dtype, key
+        assert np.abs(got.astype(np.float64) - g[key]).max() <= tol, (key, np.abs(got.astype(np.float64) - g[key]).max())
+    c2 = SamplingCoords(16, a, res, builder="native")
+    assert np.array_equal(c2.cortical.numpy(), c.cortical.numpy()) and np.array_equal(c2.cartesian_pad_coords.numpy(), c.cartesian_pad_coords.numpy())
+    # the layer chain built from it keeps the builder and the reference's point counts
+    nxt, rings, _ = c.get_strided_coords(2, auto_match_cart_resources=1, in_cart_res=64)
+    ref_next, ref_rings, _ = SamplingCoords(16, a, res, builder="torch").get_strided_coords(2, auto_match_cart_resources=1, in_cart_res=64)
+    assert nxt.builder == "native" and rings == ref_rings and len(nxt) == len(ref_next)
+
+
+def test_native_geometry_argument_checks():
+    from fovi_b200._lib import lib
+    assert lib.fovi_sensor_ring_layout(16.0, 1.0, 0, None, None) < 0 and lib.fovi_sensor_ring_layout(16.0, -1.0, 8, None, None) < 0
+    assert lib.fovi_sensor_ring_layout(16.0, 1.0, 1, None, None) == 1
+    assert lib.fovi_sensor_pad_points(16.0, 1.0, 1, 1.0, 0.5, 0, None, None) < 0
+
+
 def test_config3_layer_chain_tables_bit_exact(golden):
     t = golden("config3_tables.npz")
     strides, ks = [2, 2, 1, 1, 1], [121, 25, 9, 9, 9]
