@@ -73,6 +73,12 @@ class KNNConvLayer(nn.Module):
     ``tables_override`` = dict(knn_indices [K,n_out] int64, tap [n_out,K], V, ref_coords?) skips the
     table construction (used to run recorded tables).  ``table_builder`` ('torch' | 'native', default from
     ``tables.default_builder()``) selects how the tables are built (see fovi_b200/tables.py).
+
+    Inputs of a layer with at most 4 input channels (a first layer fed by the sensor) must be finite on the bf16 path:
+    there the two points of an aligned pair (2p, 2p+1) share one operand block, the non-neighbour multiplied by zero
+    weights, so an Inf / NaN would also reach outputs whose neighbourhoods hold only the point's partner (and the
+    neighbouring output points that share an accumulator with them).  Layers with more
+    channels, and ``precision='fp32'``, confine a non-finite input to the neighbourhoods that contain it, as the reference does.
     """
 
     def __init__(self, in_channels, out_channels, k, in_coords, out_coords, device="cuda", arch_flag="", sample_cortex=True,

@@ -128,6 +128,11 @@ int fovi_sampler_check(fovi_sampler_plan* plan, void* stream);
  * shared linear map over Cin*V (knn.py:555), evaluated as
  *   out[b,n,o] = bias[o] + sum_k sum_c X[b, idx[k,n], c] * W[o, c*V + tap[n,k]]
  * with pad neighbours (idx == n_in) skipped.
+ * Non-finite inputs: on the channels-last layout (FOVI_X_BNC) an Inf / NaN at an input point reaches exactly the outputs
+ * whose neighbourhoods contain the point, as in the reference.  On the pair layout (FOVI_X_PAIRS, c_in <= 4) the two points
+ * of a pair (2p, 2p+1) are multiplied together, the one that is not a neighbour by zero weights, so a non-finite value also
+ * reaches the outputs whose neighbourhoods contain only the point's pair partner, and with a grouped plan the other output
+ * points of the group (0 * Inf = NaN): pair-layout inputs (images) must be finite.
  * ------------------------------------------------------------------------------------------ */
 typedef struct fovi_knnconv_plan fovi_knnconv_plan;
 

@@ -197,6 +197,40 @@ def test_scatter_add_output(ops, B, Cin, Nin, Nout, K, V, Cout):
     assert np.abs(got - want).max() < 2e-3 * max(1.0, np.abs(want).max()), np.abs(got - want).max()
 
 
+@pytest.mark.parametrize("Cin,Cout", [(3, 32), (64, 64)])
+def test_non_finite_input_reaches_only_its_neighbourhoods(ops, Cin, Cout):
+    """A NaN at one input point: outputs whose neighbourhoods contain it are NaN, as in the reference (the gather of
+    knn.py:484-503 followed by the linear map); outputs whose neighbourhoods contain neither the point nor, on the pair
+    layout of a <= 4-channel layer, its pair partner are bit-identical to the clean run; no other output may change on the
+    channels-last layout."""
+    rs = np.random.RandomState(11)
+    B, Nin, Nout, K, V = 6, 40, 19, 5, 9
+    x = rs.standard_normal((B, Cin, Nin)).astype(f32)
+    idx = np.stack([rs.choice(Nin, K, replace=False) for _ in range(Nout)], 1).astype(np.int32)
+    tap = rs.randint(0, V, (Nout, K)).astype(np.uint16)
+    w = (rs.standard_normal((Cout, Cin * V)) / np.sqrt(Cin * K)).astype(f32)
+    plan = ops.KnnConvPlan(idx, tap, Nin, V, Cin, Cout)
+    clean = run_tc(ops, plan, x, w)
+    m = 7
+    bad = x.copy()
+    bad[2, 0, m] = np.nan
+    y = run_tc(ops, plan, bad, w)
+    has_m = (idx == m).any(0)
+    has_partner = (idx == (m ^ 1)).any(0)
+    assert np.isnan(y[2][:, has_m]).all()
+    if plan.x_layout == ops.X_PAIRS:
+        touched = has_m | has_partner
+        G = max(1, int(plan.group))          # consecutive output points that share an accumulator share their operand blocks
+        for g0 in range(0, Nout, G):
+            touched[g0:g0 + G] = touched[g0:g0 + G].any()
+        untouched = ~touched
+    else:
+        untouched = ~has_m
+    assert np.array_equal(y[2][:, untouched], clean[2][:, untouched])
+    other = [b for b in range(B) if b != 2]
+    assert np.array_equal(y[other], clean[other])
+
+
 def test_linearity_and_determinism_full_batch(ops, golden):
     """Size-independent properties at a full batch tile count: f(x1 + x2) == f(x1) + f(x2) without
     bias, and two runs give the same bits."""
