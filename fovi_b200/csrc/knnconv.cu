@@ -52,24 +52,30 @@ template <typename TW>
 __global__ void pack_weights_grouped_kernel(const TW* __restrict__ W, __nv_bfloat16* __restrict__ dst,
                                             const uint16_t* __restrict__ pair_tap, const uint16_t* __restrict__ member_tap, int n_groups,
                                             int sp, int K, int G, int V, int co, int c_in, int ct) {
+  // one thread per 16-byte row of the destination (a pair slot of one output channel: 2 points x 4 channels), so the
+  // index arithmetic and the two table look-ups are paid once per eight values and the store is a whole 16-byte piece
   const int c_out = G * co;
-  const long long total = (long long)n_groups * sp * c_out * 8;
+  const long long total = (long long)n_groups * sp * c_out;
   const int n_ct = c_out / ct;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int e = (int)(i & 7);
-    long long r = i >> 3;
+    long long r = i;
     const int oc = (int)(r % ct); r /= ct;
     const int sl = (int)(r % sp); r /= sp;
     const int tile = (int)(r % n_ct);
     const long long g = r / n_ct;
     const int op = tile * ct + oc;          // channel of the group: member j, its channel o
     const int j = op / co, o = op - j * co;
-    const int h = e >> 2, c = e & 3;
-    const int k = pair_tap[(g * sp + sl) * 2 + h];
-    int t = 0xFFFF;
-    if (k != 0xFFFF) t = member_tap[(g * K + k) * G + j];
-    const float w = (c < c_in && t != 0xFFFF) ? ld_as_float(W + ((long long)o * c_in + c) * V + t) : 0.f;
-    dst[i] = __float2bfloat16_rn(w);
+    __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int k = pair_tap[(g * sp + sl) * 2 + h];
+      int t = 0xFFFF;
+      if (k != 0xFFFF) t = member_tap[(g * K + k) * G + j];
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        v[h * 4 + c] = __float2bfloat16_rn((c < c_in && t != 0xFFFF) ? ld_as_float(W + ((long long)o * c_in + c) * V + t) : 0.f);
+    }
+    *reinterpret_cast<uint4*>(dst + i * 8) = *reinterpret_cast<const uint4*>(v);
   }
 }
 
@@ -316,7 +322,7 @@ extern "C" int fovi_knnconv_pack_weights_grouped(const fovi_knnconv_plan* p, con
   if (!p || !W || !member_tap || !dst || !fovi::valid_dtype(w_dtype) || G <= 0 || V <= 0) return FOVI_ERR_INVALID_ARGUMENT;
   if (p->x_layout != FOVI_X_PAIRS || !p->ct || p->c_out % G) return FOVI_ERR_UNSUPPORTED;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const long long tot = (long long)p->n_out * p->sp * p->c_out * 8;
+  const long long tot = (long long)p->n_out * p->sp * p->c_out;   // 16-byte rows
   const int grid = (int)std::min<long long>((tot + 255) / 256, 148 * 32);
   if (w_dtype == FOVI_F32)
     pack_weights_grouped_kernel<float><<<grid, 256, 0, st>>>((const float*)W, (__nv_bfloat16*)dst, p->pair_tap, member_tap, p->n_out, p->sp, p->K,
