@@ -49,6 +49,7 @@ SIGNATURES = {
     "fovi_sensor_points": (C.c_int, [C.c_double, C.c_double, C.c_int, C.c_double, C.c_longlong, _P, _P, _P]),
     "fovi_sensor_pad_points": (C.c_longlong, [C.c_double, C.c_double, C.c_int, C.c_double, C.c_double, C.c_longlong, _P, _P]),
     "fovi_column_sum": (C.c_int, [_P, C.c_int, C.c_longlong, C.c_int, _P, _P]),
+    "fovi_relu_backward_to_inner": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, _P, _P, C.c_int, C.c_int, _P, _P]),
     "fovi_tap_segment_sum": (C.c_int, [_P, C.c_int, C.c_longlong, _P, _P, C.c_int, _P, C.c_int, _P]),
     "fovi_batch_to_inner": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong, C.c_longlong, _P, C.c_int, C.c_int, _P]),
     "fovi_knn_table_build": (C.c_int, [_P, C.c_int, C.c_int, _P, C.c_int, C.c_int, _P, _P]),

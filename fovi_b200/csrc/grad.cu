@@ -35,19 +35,28 @@ __global__ void batch_to_inner_kernel(const T* __restrict__ src, __nv_bfloat16* 
 
 // Same, 64x64 tiles with two elements per access: a warp reads 64 consecutive source elements per row and writes 64 consecutive
 // batch entries (128 bytes) per row.  Needs an even fast extent and even strides (so that pairs are aligned).
+// Optionally fused, for the backward pass of a layer with a fused ReLU (src = upstream gradient, `act` = the layer's
+// output, same layout): the gradient is masked where the output is not positive before it is transposed, the masked
+// gradient is also written back in the source layout (`masked`, for the input-gradient GEMM) and its sums over
+// everything but the fast index (the channels: the bias gradient) are added into `colsum` -- one read of the gradient
+// instead of three.
 template <typename T, bool FAST_I>
 __global__ void __launch_bounds__(256) batch_to_inner_x2_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst, int B, int I, int J,
-                                                               int Jp, int Bp, long long sb, long long si, long long sj) {
+                                                               int Jp, int Bp, long long sb, long long si, long long sj,
+                                                               const T* __restrict__ act, T* __restrict__ masked, float* __restrict__ colsum) {
   __shared__ __nv_bfloat16 tile[64][66];
+  __shared__ float part[8][64];
   const int b0 = blockIdx.x * 64, f0 = blockIdx.y * 64, slow = blockIdx.z;
   const int F = FAST_I ? I : J;
   const int tx = threadIdx.x, ty = threadIdx.y;
+  float s0 = 0.f, s1 = 0.f;
   for (int r = ty; r < 64; r += 8) {
     const int b = b0 + r, f = f0 + 2 * tx;
     const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
     float v0 = 0.f, v1 = 0.f;
     if (b < B && f < F && j < J) {   // F is even: f + 1 < F as well
-      const T* p = src + b * sb + i * si + j * sj;
+      const long long off = b * sb + i * si + j * sj;
+      const T* p = src + off;
       if (sizeof(T) == 2) {
         const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(p);
         v0 = __bfloat162float(q.x); v1 = __bfloat162float(q.y);
@@ -55,11 +64,41 @@ __global__ void __launch_bounds__(256) batch_to_inner_x2_kernel(const T* __restr
         const float2 q = *reinterpret_cast<const float2*>(p);
         v0 = q.x; v1 = q.y;
       }
+      if (act) {
+        float a0, a1;
+        if (sizeof(T) == 2) {
+          const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(act + off);
+          a0 = __bfloat162float(q.x); a1 = __bfloat162float(q.y);
+        } else {
+          const float2 q = *reinterpret_cast<const float2*>(act + off);
+          a0 = q.x; a1 = q.y;
+        }
+        v0 = a0 > 0.f ? v0 : 0.f; v1 = a1 > 0.f ? v1 : 0.f;
+      }
+      if (masked) {
+        if (sizeof(T) == 2) {
+          __nv_bfloat162 q;
+          q.x = __float2bfloat16_rn(v0); q.y = __float2bfloat16_rn(v1);
+          *reinterpret_cast<__nv_bfloat162*>(masked + off) = q;
+        } else {
+          *reinterpret_cast<float2*>(masked + off) = make_float2(v0, v1);
+        }
+      }
+      s0 += v0; s1 += v1;
     }
     tile[r][2 * tx] = __float2bfloat16_rn(v0);
     tile[r][2 * tx + 1] = __float2bfloat16_rn(v1);
   }
+  if (colsum) { part[ty][2 * tx] = s0; part[ty][2 * tx + 1] = s1; }
   __syncthreads();
+  if (colsum && ty == 0) {
+    for (int e = 0; e < 2; ++e) {
+      float t = 0.f;
+      for (int w = 0; w < 8; ++w) t += part[w][2 * tx + e];
+      const int f = f0 + 2 * tx + e;
+      if (f < F) atomicAdd(colsum + f, t);
+    }
+  }
   const int Fd = FAST_I ? I : Jp;
   for (int r = ty; r < 64; r += 8) {
     const int f = f0 + r, b = b0 + 2 * tx;
@@ -159,11 +198,12 @@ extern "C" int fovi_column_sum(const void* src, int dtype, long long R, int C, f
   return fovi::after_launch("column_sum_kernel");
 }
 
-extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst,
-                                   int Jp, int Bp, void* stream) {
+static int batch_to_inner_impl(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst, int Jp, int Bp,
+                               const void* act, void* masked, float* colsum, void* stream) {
   if (!fovi::valid_dtype(dtype) || B < 0 || I <= 0 || J <= 0 || Jp < J || Bp < B || Bp <= 0) return FOVI_ERR_INVALID_ARGUMENT;
   if (!src || !dst) return FOVI_ERR_INVALID_ARGUMENT;
   if (si != 1 && sj != 1) return FOVI_ERR_UNSUPPORTED;
+  const bool fused = act || masked || colsum;
   const bool fast_i = si == 1 && !(sj == 1 && J >= I);
   const int fast = fast_i ? I : Jp, slow = fast_i ? Jp : I;
   if (slow > 65535 || (fast + 31) / 32 > 65535) return FOVI_ERR_UNSUPPORTED;
@@ -172,9 +212,16 @@ extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int
   const size_t esz = fovi::dtype_size(dtype);
   const bool x2 = F % 2 == 0 && Bp % 2 == 0 && sb % 2 == 0 && (fast_i ? sj : si) % 2 == 0 &&
                   reinterpret_cast<uintptr_t>(src) % (2 * esz) == 0 && reinterpret_cast<uintptr_t>(dst) % 4 == 0 && (fast + 63) / 64 <= 65535;
+  if (fused) {
+    // the fused form exists for the two-element kernel only; the masked copy and the activations share the source's layout
+    if (!x2 || (act && reinterpret_cast<uintptr_t>(act) % (2 * esz)) || (masked && reinterpret_cast<uintptr_t>(masked) % (2 * esz)))
+      return FOVI_ERR_UNSUPPORTED;
+    if (colsum) FOVI_CUDA(cudaMemsetAsync(colsum, 0, sizeof(float) * (size_t)F, st));
+  }
   if (x2) {
     dim3 grid2((Bp + 63) / 64, (fast + 63) / 64, slow), block2(32, 8);
-#define RUN2(T, FI) batch_to_inner_x2_kernel<T, FI><<<grid2, block2, 0, st>>>((const T*)src, (__nv_bfloat16*)dst, B, I, J, Jp, Bp, sb, si, sj)
+#define RUN2(T, FI) batch_to_inner_x2_kernel<T, FI><<<grid2, block2, 0, st>>>((const T*)src, (__nv_bfloat16*)dst, B, I, J, Jp, Bp, sb, si, sj, \
+                                                                              (const T*)act, (T*)masked, colsum)
     if (dtype == FOVI_F32) { if (fast_i) RUN2(float, true); else RUN2(float, false); }
     else { if (fast_i) RUN2(__nv_bfloat16, true); else RUN2(__nv_bfloat16, false); }
 #undef RUN2
@@ -186,4 +233,15 @@ extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int
   else { if (fast_i) RUN(__nv_bfloat16, true); else RUN(__nv_bfloat16, false); }
 #undef RUN
   return fovi::after_launch("batch_to_inner_kernel");
+}
+
+extern "C" int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst,
+                                   int Jp, int Bp, void* stream) {
+  return batch_to_inner_impl(src, dtype, B, I, J, sb, si, sj, dst, Jp, Bp, nullptr, nullptr, nullptr, stream);
+}
+
+extern "C" int fovi_relu_backward_to_inner(const void* grad, const void* act, int dtype, int B, int I, int J, long long sb, long long si,
+                                           long long sj, void* masked, void* dst, int Jp, int Bp, float* colsum, void* stream) {
+  if (!act && !masked && !colsum) return FOVI_ERR_INVALID_ARGUMENT;
+  return batch_to_inner_impl(grad, dtype, B, I, J, sb, si, sj, dst, Jp, Bp, act, masked, colsum, stream);
 }

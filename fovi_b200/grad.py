@@ -149,13 +149,13 @@ class KnnConvGrad:
             self._dw_plans[key] = plan
         return self._dw_plans[key]
 
-    def _weight_grad_few(self, gy, x):
+    def _weight_grad_few(self, gy, x, gy_inner=None):
         B = gy.shape[0]
         bp = -(-B // 64) * 64
         if self._few is None:
             self._few = self._few_tables(self._idx, self._tap)
         kp, gather = self._few
-        gy_t = ops.batch_to_inner(gy, bp=bp)                                            # [c_out, n_out, bp]
+        gy_t = gy_inner if gy_inner is not None else ops.batch_to_inner(gy, bp=bp)      # [c_out, n_out, bp]
         x_t = torch.zeros((self.n_in + 1, 4, bp), dtype=torch.bfloat16, device=x.device)
         ops.batch_to_inner(x.permute(0, 2, 1), jp=4, bp=bp, out=x_t[:self.n_in])        # [n_in (+ zero row), 4, bp]
         dw = torch.zeros((self.c_out, self.V * 4), dtype=torch.float32, device=gy.device)
@@ -168,21 +168,27 @@ class KnnConvGrad:
             ops.tap_segment_sum(prod.view(self.c_out, npts * kp, 4), seg_start, seg_slot, dw)   # every tap sums its pairs
         return dw.reshape(self.c_out, self.V, 4)[:, :, :self.c_in].permute(0, 2, 1).reshape(self.c_out, self.c_in * self.V)
 
-    def weight_grad(self, gy, x):
-        """gy [B, c_out, n_out] and x [B, c_in, n_in] (any strides/dtype) -> dW [c_out, c_in*V] float32."""
+    def gy_inner_view(self, gy_points):
+        """The view of the upstream gradient ([B, n_out, c_out], channels last) whose batch-innermost copy `weight_grad`
+        wants: logical [B, I, J] with dst [I, J, bp] = [c_out, n_out, bp], or [n_out, c_out, bp] for a turned GEMM."""
+        return gy_points if (self.dw_swapped and self.c_in > 4) else gy_points.permute(0, 2, 1)
+
+    def weight_grad(self, gy, x, gy_inner=None):
+        """gy [B, c_out, n_out] and x [B, c_in, n_in] (any strides/dtype) -> dW [c_out, c_in*V] float32.
+        `gy_inner`: the batch-innermost copy of gy (see gy_inner_view), when the caller already has it."""
         if self.c_in <= 4:
-            return self._weight_grad_few(gy, x)
+            return self._weight_grad_few(gy, x, gy_inner)
         B = gy.shape[0]
         bp = -(-B // 64) * 64
         plan, owner = self.dw_plan(bp)
         # every part of a tap's list is reduced into the tap's rows by the kernel's epilogue (float32 reductions in L2)
         if self.dw_swapped:
             x_r = ops.batch_to_inner(x, bp=bp)                                          # rows: [c_in, n_in, bp]
-            gy_w = ops.batch_to_inner(gy.permute(0, 2, 1), jp=self.c_out, bp=bp)        # "weights": [n_out, c_out, bp]
+            gy_w = gy_inner if gy_inner is not None else ops.batch_to_inner(gy.permute(0, 2, 1), jp=self.c_out, bp=bp)   # "weights": [n_out, c_out, bp]
             dw_t = torch.zeros((self.c_in, self.V, self.c_out), dtype=torch.float32, device=gy.device)
             plan.forward_scatter_add(x_r, gy_w, owner, dw_t)
             return dw_t.permute(2, 0, 1).reshape(self.c_out, self.c_in * self.V)
-        gy_t = ops.batch_to_inner(gy, bp=bp)                                           # rows: [c_out, n_out, bp]
+        gy_t = gy_inner if gy_inner is not None else ops.batch_to_inner(gy, bp=bp)     # rows: [c_out, n_out, bp]
         x_t = ops.batch_to_inner(x.permute(0, 2, 1), jp=self.c_in_pad, bp=bp)          # "weights": [n_in, c_in_pad, bp]
         dw = torch.zeros((self.c_out, self.V, self.c_in_pad), dtype=torch.float32, device=gy.device)
         plan.forward_scatter_add(gy_t, x_t, owner, dw)
@@ -235,17 +241,29 @@ class _KnnConvPointsFunction(torch.autograd.Function):
         x, weight, y = ctx.saved_tensors
         g = ctx.layer.grad_plans
         gy = gy.to(torch.bfloat16)
-        if ctx.relu:
-            gy = torch.ops.aten.threshold_backward(gy, y, 0)       # gy where y > 0, else 0: one pass
-        gy = gy.contiguous()
-        gx = gw = gb = None
+        want_w, want_b = ctx.needs_input_grad[1], ctx.has_bias and ctx.needs_input_grad[2]
+        gy_inner = gb = None
+        if ctx.relu and want_w and gy.is_contiguous():
+            # ReLU mask, bias sums and the batch-innermost copy the weight gradient needs, in one pass over the gradient
+            bp = -(-gy.shape[0] // 64) * 64
+            view = g.gy_inner_view(gy)
+            fused = ops.relu_backward_to_inner(view, g.gy_inner_view(y), bp=bp, want_masked=ctx.needs_input_grad[0],
+                                               want_colsum=want_b)    # the sums run over all but the contiguous index: per channel
+            if fused is not None:
+                masked, gy_inner, gb = fused
+                gy = gy if masked is None else (masked if view is gy else masked.permute(0, 2, 1))
+        if gy_inner is None:
+            if ctx.relu:
+                gy = torch.ops.aten.threshold_backward(gy, y, 0)       # gy where y > 0, else 0: one pass
+            gy = gy.contiguous()
+        gx = gw = None
         if ctx.needs_input_grad[0]:
             if ctx.first:
                 raise NotImplementedError("input gradient of a pair-layout first layer is not built")
             gx = g.input_grad(gy, weight)                                      # [B, n_in, c_in] bf16
-        if ctx.needs_input_grad[1]:
-            gw = g.weight_grad(gy.permute(0, 2, 1), x if ctx.first else x.permute(0, 2, 1)).to(weight.dtype)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
+        if want_w:
+            gw = g.weight_grad(gy.permute(0, 2, 1), x if ctx.first else x.permute(0, 2, 1), gy_inner=gy_inner).to(weight.dtype)
+        if want_b and gb is None:
             gb = ops.column_sum(gy) if gy.shape[-1] % 2 == 0 else gy.sum((0, 1), dtype=torch.float32)
         return gx, gw, gb, None, None
 

@@ -474,6 +474,30 @@ def batch_to_inner(src, jp=None, bp=None, out=None):
     return out
 
 
+def relu_backward_to_inner(grad, act, jp=None, bp=None, want_masked=True, want_colsum=True):
+    """Fused start of a layer's backward pass.  grad / act: logical [B, I, J] tensors of the same dtype and strides (one
+    of the last two contiguous).  Returns (masked gradient in grad's layout or None, [I, jp, bp] bf16 batch-innermost copy
+    of the masked gradient, float32 sums over everything but the contiguous index or None), or None when the shapes need
+    the separate calls (odd extents or strides)."""
+    _need_cuda(grad, act)
+    B, I, J = grad.shape
+    jp, bp = J if jp is None else int(jp), B if bp is None else int(bp)
+    sb, si, sj = grad.stride()
+    if (si != 1 and sj != 1) or act.stride() != grad.stride() or act.dtype != grad.dtype or act.shape != grad.shape:
+        return None
+    F = I if (si == 1 and not (sj == 1 and J >= I)) else J
+    masked = torch.empty_strided(grad.shape, grad.stride(), dtype=grad.dtype, device=grad.device) if want_masked else None
+    out = torch.empty((I, jp, bp), dtype=torch.bfloat16, device=grad.device)
+    colsum = torch.empty(F, dtype=torch.float32, device=grad.device) if want_colsum else None
+    with torch.cuda.device(grad.device):
+        rc = lib.fovi_relu_backward_to_inner(_ptr(grad), _ptr(act), _dt(grad.dtype), B, I, J, sb, si, sj, _ptr(masked) if masked is not None else None,
+                                             _ptr(out), jp, bp, _ptr(colsum) if colsum is not None else None, _stream())
+    if rc == 2:   # FOVI_ERR_UNSUPPORTED: shapes the fused kernel does not take
+        return None
+    check(rc, "fovi_relu_backward_to_inner")
+    return masked, out, colsum
+
+
 def column_sum(x):
     """x [..., C] contiguous float32/bf16 CUDA tensor -> float32 [C]: the sum over all leading dimensions."""
     _need_cuda(x)

@@ -286,6 +286,15 @@ int fovi_knn_depthwise_backward(const fovi_knnconv_plan* plan, const void* X, in
 int fovi_batch_to_inner(const void* src, int dtype, int B, int I, int J, long long sb, long long si, long long sj, void* dst, int Jp,
                         int Bp, void* stream);
 
+/* fovi_batch_to_inner fused with the first steps of a layer's backward pass (fovi_b200/grad.py): `grad` is the upstream
+ * gradient and `act` (may be NULL: no ReLU) the layer's output in the same layout and dtype; the gradient is zeroed where the
+ * output is not positive (ReLU backward), written back in the source layout to `masked` (may be NULL), transposed to `dst`
+ * like fovi_batch_to_inner, and summed over everything but the contiguous source index into colsum (float32, one entry per
+ * value of that index: the bias gradient when the channels are contiguous; may be NULL; zeroed here).  Needs even extents and
+ * strides (FOVI_ERR_UNSUPPORTED otherwise: use the separate calls). */
+int fovi_relu_backward_to_inner(const void* grad, const void* act, int dtype, int B, int I, int J, long long sb, long long si,
+                                long long sj, void* masked, void* dst, int Jp, int Bp, float* colsum, void* stream);
+
 /* Bias gradient: dst[c] = sum over the R rows of the row-major [R, C] matrix src (bf16 or float32, C even), float32
  * accumulation; dst is overwritten.  (The reference: autograd of the bias add in F.linear, fovi/arch/knn.py:555.) */
 int fovi_column_sum(const void* src, int dtype, long long R, int C, float* dst, void* stream);
