@@ -15,7 +15,9 @@ themselves table-driven gather-GEMMs, so each runs as a forward launch of ``fovi
   split and the parts added into their tap's rows by the kernel's epilogue.  Layers with at most 4 input channels use one GEMM per output point instead (see
   ``_weight_grad_few``).
 
-Operands are bf16 with float32 accumulation, as under the reference's autocast training.
+Operands are bf16 with float32 accumulation, as under the reference's autocast training.  Layers that run on the exact
+float32 kernel (``precision='fp32'``, or shapes outside the tensor-core kernel) take the same two derived layers through
+that kernel instead (``input_grad_f32`` / ``weight_grad_f32``): float32 arithmetic throughout, for parity work, not speed.
 """
 import numpy as np
 import torch
@@ -114,6 +116,48 @@ class KnnConvGrad:
             self._dw_plans[bp] = (plan, torch.from_numpy(np.ascontiguousarray(owner, dtype=np.int32)).to(self.device))
         return self._dw_plans[bp]
 
+    # ---- exact float32 route (precision='fp32' layers and shapes outside the tensor-core kernel): the same two derived
+    # layers, run on the exact float32 kernel (fovi_knnconv_forward_f32) instead of the tensor cores
+    def _f32_plans(self, B):
+        key = ("f32", B)
+        if key not in self._dw_plans:
+            order, gid, pos, _, _ = _grouped(self._m, self.n_in)
+            kt = max(1, int(pos.max()) + 1 if pos.size else 1)
+            idx_t = np.full((kt, self.n_in), self.n_out, np.int32)
+            tap_t = np.zeros((self.n_in, kt), np.uint16)
+            idx_t[pos, gid] = self._n[order]
+            tap_t[gid, pos] = self._v[order]
+            dx = ops.KnnConvPlan(idx_t, tap_t, self.n_out, self.V, self.c_out, self.c_in, device=self.device)
+            order, gid, pos, n_groups, parts = _grouped(self._v, self.V, 512)
+            kw = max(1, int(pos.max()) + 1 if pos.size else 1)
+            idx_w = np.full((kw, n_groups), self.n_out, np.int32)
+            tap_w = np.zeros((n_groups, kw), np.uint16)
+            idx_w[pos, gid] = self._n[order]
+            tap_w[gid, pos] = self._m[order]
+            dw = ops.KnnConvPlan(idx_w, tap_w, self.n_out, self.n_in, B, self.c_in, device=self.device)
+            owner = np.arange(n_groups) // parts if isinstance(parts, int) else parts
+            self._dw_plans[key] = (dx, dw, torch.from_numpy(np.ascontiguousarray(owner, dtype=np.int64)).to(self.device))
+        return self._dw_plans[key]
+
+    def input_grad_f32(self, gy, weight):
+        """gy [B, c_out, n_out], weight [c_out, c_in*V] -> dX [B, c_in, n_in], float32 arithmetic throughout."""
+        dx, _, _ = self._f32_plans(gy.shape[0])
+        w_t = weight.detach().float().reshape(self.c_out, self.c_in, self.V).permute(1, 0, 2).reshape(self.c_in, self.c_out * self.V)
+        return dx.forward_f32(gy.float(), dx.pack_weights(w_t.contiguous(), dtype=torch.float32))
+
+    def weight_grad_f32(self, gy, x):
+        """gy [B, c_out, n_out], x [B, c_in, n_in] -> dW [c_out, c_in*V] float32: rows = output channels, "channels" = the
+        batch, "taps" = the input points holding X^T, one pseudo output point per part of a filter tap's pair list."""
+        B = gy.shape[0]
+        _, dw, owner = self._f32_plans(B)
+        rows = gy.float().permute(1, 0, 2).contiguous()                               # [c_out, B, n_out]
+        taps = torch.zeros((self.n_in, self.c_in, dw.cin_packed), dtype=torch.float32, device=gy.device)
+        taps[:, :, :B] = x.float().permute(2, 1, 0)                                   # [n_in, c_in, B]
+        parts = dw.forward_f32(rows, taps)                                            # [c_out, c_in, parts]
+        out = torch.zeros((self.c_out, self.c_in, self.V), dtype=torch.float32, device=gy.device)
+        out.index_add_(2, owner, parts)
+        return out.reshape(self.c_out, self.c_in * self.V)
+
     # ---- dW of a layer with at most 4 input channels
     # One tap's pair list would give MMAs of only c_in columns (a 64x3 outer product per pair fills 9 % of an MMA).  Instead
     # there is one GEMM per output point n: rows = output channels, columns = (neighbour k, channel c), contraction over the
@@ -209,6 +253,14 @@ class _KnnConvFunction(torch.autograd.Function):
         x, weight = ctx.saved_tensors
         g = ctx.layer.grad_plans
         gx = gw = gb = None
+        if ctx.layer.precision == "fp32" or not ctx.layer.plan.tc_supported:      # the forward ran on the exact float32 kernel
+            if ctx.needs_input_grad[0]:
+                gx = g.input_grad_f32(gy, weight).to(x.dtype)
+            if ctx.needs_input_grad[1]:
+                gw = g.weight_grad_f32(gy, x).to(weight.dtype)
+            if ctx.has_bias and ctx.needs_input_grad[2]:
+                gb = gy.sum((0, 2), dtype=torch.float32)
+            return gx, gw, gb, None
         if ctx.needs_input_grad[0]:
             gyp = gy.permute(0, 2, 1).to(torch.bfloat16).contiguous()
             gx = g.input_grad(gyp, weight).permute(0, 2, 1).to(x.dtype)

@@ -7,7 +7,6 @@ tensor-core kernel (bf16 operands, fp32 accumulation) or, with ``precision='fp32
 float32 kernel.  With gradients enabled the bf16 path is differentiable (fovi_b200/grad.py: both gradient
 contractions run on the same kernel).
 """
-import warnings
 
 import numpy as np
 import torch
@@ -124,7 +123,6 @@ class KNNConvLayer(nn.Module):
                                      n_in, V, in_channels, out_channels, device=dev)
         self._packed = {}          # dtype -> (weight version, data_ptr, packed tensor)
         self._grad = None
-        self._warned_no_grad = False
 
     # ---- tables in the reference's own representation, built on demand (can be hundreds of MB)
     @property
@@ -167,18 +165,8 @@ class KNNConvLayer(nn.Module):
         """X_l [B,C_in,N_in] -> [B,C_out,N_out] in X_l's dtype (knn.py:538-557); the result is a
         channels-last view."""
         if torch.is_grad_enabled() and (X_l.requires_grad or self.weight.requires_grad or (self.bias is not None and self.bias.requires_grad)):
-            if self.precision == "bf16" and self._plan.tc_supported:
-                from .grad import knnconv_autograd
-                return knnconv_autograd(self, X_l)
-            if X_l.requires_grad:
-                raise RuntimeError("the backward pass is built for the bf16 tensor-core path: call this layer under torch.no_grad()")
-            # Only parameters want gradients and this configuration has no backward: the result carries no grad_fn, so
-            # this layer would silently stay untrained while layers behind it learn.  Say so (once per layer).
-            if not self._warned_no_grad:
-                self._warned_no_grad = True
-                warnings.warn(f"{self.__class__.__name__}: parameters require grad but this configuration (precision={self.precision!r}, "
-                              f"tensor-core path {'available' if self._plan.tc_supported else 'unavailable'}) has no backward pass; "
-                              "the output is detached and these parameters will not be trained", RuntimeWarning, stacklevel=2)
+            from .grad import knnconv_autograd
+            return knnconv_autograd(self, X_l)      # tensor-core gradients, or the exact float32 ones for precision='fp32'
         with torch.no_grad():
             return self._forward(X_l)
 

@@ -176,21 +176,51 @@ def test_column_sum(shape, dtype):
     assert float((got.double() - want).abs().max()) <= 1e-5 * scale
 
 
-def test_layer_without_backward_warns_instead_of_silently_detaching():
-    """precision='fp32' has no backward pass: with trainable parameters and a plain input the layer says so once."""
-    import warnings
+def test_float32_layer_gradients_match_reference_autograd(golden):
+    """precision='fp32': forward and both gradient contractions run on the exact float32 kernel; against the reference's
+    autograd in float32 the agreement is at float32 rounding, not at bf16's."""
+    from fovi_b200.knn import KNNConvLayer
+    g = golden("backward_small.npz")
+    V, n_in = int(g["V"]), int(g["n_in"])
+    rs = np.random.RandomState(int(g["seed"]))
+    w = kaiming_weight(rs, 32, 16, V)
+    b = (0.1 * rs.standard_normal(32)).astype(np.float32)
+    x = rs.standard_normal((5, 16, n_in)).astype(np.float32)
+    gy = rs.standard_normal((5, 32, g["knn_idx"].shape[1])).astype(np.float32)
+    layer = KNNConvLayer(16, 32, g["knn_idx"].shape[0], _Pts(n_in), _Pts(g["knn_idx"].shape[1]), device="cuda", bias=True, precision="fp32",
+                         tables_override=dict(knn_indices=g["knn_idx"], tap=g["tap"], V=V))
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(w))
+        layer.bias.copy_(torch.from_numpy(b))
+    xt = torch.from_numpy(x).cuda().requires_grad_(True)
+    y = layer(xt)
+    assert y.requires_grad and rel_l2(y.detach().cpu().numpy(), g["y"]) < 1e-5
+    y.backward(torch.from_numpy(gy).cuda())
+    assert rel_l2(xt.grad.cpu().numpy(), g["dX"]) < 1e-5
+    assert rel_l2(layer.weight.grad.cpu().numpy(), g["dW"]) < 1e-5
+    assert rel_l2(layer.bias.grad.cpu().numpy(), g["dbias"]) < 1e-5
+    # parameters only (a plain input): the result still carries the graph
+    layer.weight.grad = None
+    y2 = layer(torch.from_numpy(x).cuda())
+    assert y2.grad_fn is not None
+    y2.backward(torch.from_numpy(gy).cuda())
+    assert rel_l2(layer.weight.grad.cpu().numpy(), g["dW"]) < 1e-5
+
+
+def test_float32_first_layer_trains():
+    """A 3-channel float32 layer built from its own tables: gradients against the oracle's backward (float64)."""
     from fovi_b200.coords import get_in_out_coords
     from fovi_b200.knn import KNNConvLayer
     ic, oc, _ = get_in_out_coords(20, 16, 1.0, 2, auto_match_cart_resources=0)
-    layer = KNNConvLayer(3, 16, 9, ic, oc, device="cuda", ref_frame_side_length=3, precision="fp32")
-    x = torch.randn(2, 3, ic.shape[0], device="cuda")
-    with pytest.warns(RuntimeWarning, match="no backward pass"):
-        y = layer(x)
-    assert y.grad_fn is None
-    with warnings.catch_warnings():
-        warnings.simplefilter("error")
-        layer(x)                                    # once per layer
-        with torch.no_grad():
-            layer(x)
-    with pytest.raises(RuntimeError):
-        layer(x.requires_grad_())
+    layer = KNNConvLayer(3, 16, 9, ic, oc, device="cuda", ref_frame_side_length=3, precision="fp32", bias=True)
+    rs = np.random.RandomState(5)
+    x = rs.standard_normal((3, 3, ic.shape[0])).astype(np.float32)
+    gy = rs.standard_normal((3, 16, oc.shape[0])).astype(np.float32)
+    xt = torch.from_numpy(x).cuda().requires_grad_(True)
+    layer(xt).backward(torch.from_numpy(gy).cuda())
+    idx = layer.knn_indices_pad_token.numpy().astype(np.int64)
+    V = layer.ref_coords.shape[0]
+    dX, dW, db = oracle.knnconv_backward(x.astype(np.float64), idx, layer.tap.numpy().astype(np.int64), V,
+                                         layer.weight.detach().cpu().numpy().astype(np.float64), gy.astype(np.float64))
+    assert rel_l2(xt.grad.cpu().numpy(), dX) < 1e-5 and rel_l2(layer.weight.grad.cpu().numpy(), dW) < 1e-5
+    assert rel_l2(layer.bias.grad.cpu().numpy(), db) < 1e-5
