@@ -61,6 +61,7 @@ SIGNATURES = {
     "fovi_knn_norm_forward": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P, C.c_float, C.c_int, _P, _P,
                                         C.c_int, _P]),
     "fovi_knnpool_forward": (C.c_int, [_P, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "fovi_knnpool_backward": (C.c_int, [_P, _P, C.c_int, _P, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "fovi_launch_count": (C.c_int64, []),
 }
 

@@ -86,6 +86,50 @@ __global__ void knnpool_bnc8_kernel(const __nv_bfloat16* __restrict__ X, __nv_bf
   }
 }
 
+// Gradient of the pooling with respect to its input, what autograd computes through the reference's gather and
+// nan-aware reductions (fovi/arch/knn.py:345-394): every output element hands its upstream gradient back to the
+// neighbours it read -- 'sum': all of it to each; 'avg': 1/count to each; 'gaussian': the renormalised weight w_k /
+// (sum of valid weights + 1e-8) to each; 'max': all of it to the first neighbour (in list order) that holds the maximum.
+// One thread per output element, float32 atomic adds into a zero-initialised dX (neighbourhoods overlap).
+template <typename TX, typename TG, int MODE>
+__global__ void knnpool_backward_kernel(const TX* __restrict__ X, const TG* __restrict__ G, float* __restrict__ dX, const int* __restrict__ idx,
+                                        const float* __restrict__ wgt, int B, int C, int n_in, int n_out, int K, int bnc) {
+  const long long total = (long long)B * C * n_out;
+  for (long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    int b, c, n;
+    if (bnc) { c = (int)(e % C); n = (int)((e / C) % n_out); b = (int)(e / ((long long)C * n_out)); }
+    else { n = (int)(e % n_out); c = (int)((e / n_out) % C); b = (int)(e / ((long long)C * n_out)); }
+    const int* nb = idx + (long long)n * K;
+    const float g = ld_as_float(G + e);
+    auto at = [&](int j) { return bnc ? ((long long)b * n_in + j) * C + c : ((long long)b * C + c) * n_in + j; };
+    // first pass: what the forward reduced over (valid = not a pad, not NaN)
+    float best = -INFINITY, wsum = 0.f;
+    int cnt = 0, arg = -1;
+    for (int k = 0; k < K; ++k) {
+      const int j = __ldg(nb + k);
+      if (j >= n_in) continue;
+      const float v = ld_as_float(X + at(j));
+      if (v != v) continue;
+      if (MODE == 0 && (arg < 0 || v > best)) { best = v; arg = j; }
+      if (MODE == 3) wsum += __ldg(wgt + (long long)n * K + k);
+      ++cnt;
+    }
+    if (cnt == 0) continue;
+    if constexpr (MODE == 0) {
+      atomicAdd(dX + at(arg), g);
+    } else {
+      for (int k = 0; k < K; ++k) {
+        const int j = __ldg(nb + k);
+        if (j >= n_in) continue;
+        const float v = ld_as_float(X + at(j));
+        if (v != v) continue;
+        const float coeff = MODE == 1 ? 1.f / (float)cnt : MODE == 3 ? __ldg(wgt + (long long)n * K + k) / (wsum + 1e-8f) : 1.f;
+        atomicAdd(dX + at(j), g * coeff);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" int fovi_knnpool_plan_create(const int32_t* knn_idx_pad, int n_in, int n_out, int K, fovi_knnpool_plan** out) {
@@ -153,4 +197,26 @@ extern "C" int fovi_knnpool_forward(const fovi_knnpool_plan* p, const void* X, i
   else { if (mode == 0) RUN(__nv_bfloat16, 0); else if (mode == 1) RUN(__nv_bfloat16, 1); else if (mode == 2) RUN(__nv_bfloat16, 2); else RUN(__nv_bfloat16, 3); }
 #undef RUN
   return fovi::after_launch("knnpool_kernel");
+}
+
+extern "C" int fovi_knnpool_backward(const fovi_knnpool_plan* p, const void* X, int x_dtype, const void* gY, int g_dtype, int layout, int B, int C,
+                                     int mode, float* dX, void* stream) {
+  if (!p || !fovi::valid_dtype(x_dtype) || !fovi::valid_dtype(g_dtype) || B < 0 || C <= 0 || mode < 0 || mode > 3) return FOVI_ERR_INVALID_ARGUMENT;
+  if (mode == 3 && !p->wgt) return FOVI_ERR_INVALID_ARGUMENT;
+  if (layout != FOVI_ACT_BCN && layout != FOVI_ACT_BNC) return FOVI_ERR_INVALID_ARGUMENT;
+  if (B == 0) return FOVI_OK;
+  if (!X || !gY || !dX) return FOVI_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  FOVI_CUDA(cudaMemsetAsync(dX, 0, sizeof(float) * (size_t)B * C * p->n_in, st));
+  const long long total = (long long)B * C * p->n_out;
+  const int grid = (int)std::min<long long>((total + 255) / 256, (long long)fovi::sm_count() * 32);
+  const int bnc = layout == FOVI_ACT_BNC;
+#define RUNB(TX, TG, M) knnpool_backward_kernel<TX, TG, M><<<grid, 256, 0, st>>>((const TX*)X, (const TG*)gY, dX, p->idx, p->wgt, B, C, p->n_in, \
+                                                                                  p->n_out, p->K, bnc)
+#define RUNM(TX, TG) do { if (mode == 0) RUNB(TX, TG, 0); else if (mode == 1) RUNB(TX, TG, 1); else if (mode == 2) RUNB(TX, TG, 2); else RUNB(TX, TG, 3); } while (0)
+  if (x_dtype == FOVI_F32) { if (g_dtype == FOVI_F32) RUNM(float, float); else RUNM(float, __nv_bfloat16); }
+  else { if (g_dtype == FOVI_F32) RUNM(__nv_bfloat16, float); else RUNM(__nv_bfloat16, __nv_bfloat16); }
+#undef RUNM
+#undef RUNB
+  return fovi::after_launch("knnpool_backward_kernel");
 }

@@ -18,6 +18,23 @@ from .coords import SamplingCoords, get_in_out_coords  # noqa: F401  (re-exporte
 __all__ = ["KNNPoolingLayer", "KNNConvLayer", "KNNDepthwiseConvLayer", "KNNDepthwiseSeparableConvLayer", "KNNPatchEmbedding", "KNNPartitioningPatchEmbedding", "KNNConvStack", "KNN_CONV_REGISTRY", "get_knn_conv_layer"]
 
 
+class _PoolFunction(torch.autograd.Function):
+    """KNN pooling with its input gradient (fovi_knnpool_backward): what autograd computes through the reference's gather
+    and nan-aware reductions (fovi/arch/knn.py:345-394)."""
+
+    @staticmethod
+    def forward(ctx, x, plan, mode, layout):
+        ctx.plan, ctx.mode, ctx.layout = plan, mode, layout
+        ctx.save_for_backward(x)
+        with torch.no_grad():
+            return plan.forward(x, mode, layout)
+
+    @staticmethod
+    def backward(ctx, gy):
+        (x,) = ctx.saved_tensors
+        return ctx.plan.backward(x, gy, ctx.mode, ctx.layout).to(x.dtype), None, None, None
+
+
 class KNNPoolingLayer(nn.Module):
     """Pooling over the K nearest neighbours; counterpart of the reference layer (fovi/arch/knn.py:276-397): modes 'max',
     'avg', 'sum' and 'gaussian' (distance-weighted mean).  forward(X [B,C,N_in]) -> [B,C,N_out]."""
@@ -51,14 +68,19 @@ class KNNPoolingLayer(nn.Module):
         w = torch.exp(-k ** 2 / (2 * self.gauss_sigma ** 2))
         return w / (w.sum(dim=0, keepdim=True) + 1e-8)
 
-    @torch.no_grad()
     def forward(self, X_l):
-        return self._plan.forward(X_l, self.mode, ops.ACT_BCN)
+        """X_l [B,C,N_in] -> [B,C,N_out]; differentiable with respect to X_l."""
+        if torch.is_grad_enabled() and X_l.requires_grad:
+            return _PoolFunction.apply(X_l, self._plan, self.mode, ops.ACT_BCN)
+        with torch.no_grad():
+            return self._plan.forward(X_l, self.mode, ops.ACT_BCN)
 
-    @torch.no_grad()
     def forward_points(self, x_bnc):
-        """Channels-last [B,N_in,C] -> [B,N_out,C] (the layout between the KNNConv kernels)."""
-        return self._plan.forward(x_bnc, self.mode, ops.ACT_BNC)
+        """Channels-last [B,N_in,C] -> [B,N_out,C] (the layout between the KNNConv kernels); differentiable."""
+        if torch.is_grad_enabled() and x_bnc.requires_grad:
+            return _PoolFunction.apply(x_bnc, self._plan, self.mode, ops.ACT_BNC)
+        with torch.no_grad():
+            return self._plan.forward(x_bnc, self.mode, ops.ACT_BNC)
 
     def __repr__(self):
         return f"KNNPoolingLayer(\n\tmode={self.mode}\n\tk={self.k}\n\tin_coords={self.in_coords}\n\tout_coords={self.out_coords}\n\tsample_cortex={self.sample_cortex}\n)"

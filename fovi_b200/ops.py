@@ -412,6 +412,20 @@ class KnnPoolPlan:
         return y
 
 
+    def backward(self, x, gy, mode="max", layout=ACT_BCN):
+        """Gradient of `forward` with respect to x: x and gy in `layout` (float32 or bf16) -> float32 tensor of x's shape."""
+        _need_cuda(x, gy)
+        x, gy = x.contiguous(), gy.contiguous()
+        B = x.shape[0]
+        Cc = x.shape[1] if layout == ACT_BCN else x.shape[2]
+        assert (x.shape[2] if layout == ACT_BCN else x.shape[1]) == self.n_in and gy.shape == ((B, Cc, self.n_out) if layout == ACT_BCN else (B, self.n_out, Cc))
+        dx = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib.fovi_knnpool_backward(self._h, _ptr(x), _dt(x.dtype), _ptr(gy), _dt(gy.dtype), layout, B, Cc, POOL_MODES[mode], _ptr(dx), _stream()),
+                  "fovi_knnpool_backward")
+        return dx
+
+
 def knn_norm(x, mode, weight=None, bias=None, eps=1e-5, groups=1, layout=ACT_BCN, relu=False, out_dtype=None):
     """Per-sample normalisation of x ([B,C,N] for ACT_BCN, [B,N,C] for ACT_BNC; float32 or bf16) over the channels
     ('channel'), the points ('coord'), both ('layer') or channel groups x points ('group'); weight / bias float32 of the

@@ -370,6 +370,13 @@ int fovi_knnpool_set_weights(fovi_knnpool_plan* plan, const float* w_kn);
 int fovi_knnpool_forward(const fovi_knnpool_plan* plan, const void* X, int dtype, int layout, int B, int C, int mode,
                          void* Y, void* stream);
 
+/* Gradient of fovi_knnpool_forward with respect to X (autograd through the reference's gather and nan-aware reductions,
+ * fovi/arch/knn.py:345-394): dX (float32, X's layout and shape, overwritten) receives from every output element its
+ * upstream gradient gY, shared out to the neighbours it read -- sum: 1 each; avg: 1/count; gaussian: the renormalised
+ * weight; max: all to the first neighbour in list order holding the maximum.  Float32 atomic adds: the last bits may vary. */
+int fovi_knnpool_backward(const fovi_knnpool_plan* plan, const void* X, int x_dtype, const void* gY, int g_dtype, int layout, int B,
+                          int C, int mode, float* dX, void* stream);
+
 /* Number of kernels this library has launched from the calling process (all entry points). */
 int64_t fovi_launch_count(void);
 

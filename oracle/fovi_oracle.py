@@ -332,6 +332,37 @@ def knn_pool_weighted(X, knn_idx_pad, weights):
     return (np.where(valid, g, 0.0) * w).sum(2).astype(f32)
 
 
+def knn_pool_backward(X, knn_idx_pad, grad_out, mode, weights=None):
+    """Gradient of the KNN pooling with respect to its input (autograd through the gather and nan-aware reductions of
+    fovi/arch/knn.py:345-394): every output element gives its upstream gradient back to the valid neighbours it read --
+    'sum' 1 each, 'avg' 1/count, 'gaussian' w_k / (sum of valid w + 1e-8), 'max' all to the first neighbour in list order
+    holding the maximum.  X [B,C,n_in], grad_out [B,C,n_out] -> [B,C,n_in] float32 (float64 accumulation)."""
+    X = np.asarray(X, np.float64)
+    G = np.asarray(grad_out, np.float64)
+    K, n_out = knn_idx_pad.shape
+    n_in = X.shape[2]
+    g = _pool_gather(X, knn_idx_pad)                                   # [B,C,K,n_out], NaN at pad neighbours
+    valid = ~np.isnan(g)
+    if mode == "max":
+        first = np.argmax(np.where(valid, g, -np.inf), axis=2)         # first maximum in list order
+        coeff = (np.arange(K)[None, None, :, None] == first[:, :, None, :]) & valid.any(2, keepdims=True)
+        coeff = coeff.astype(np.float64)
+    elif mode == "sum":
+        coeff = valid.astype(np.float64)
+    elif mode == "avg":
+        coeff = valid / np.maximum(valid.sum(2, keepdims=True), 1)
+    elif mode == "gaussian":
+        w = np.where(valid, np.asarray(weights, np.float64)[None, None], 0.0)
+        coeff = w / (w.sum(2, keepdims=True) + 1e-8)
+    else:
+        raise ValueError(mode)
+    dX = np.zeros((X.shape[0], X.shape[1], n_in + 1))
+    idx = np.broadcast_to(np.asarray(knn_idx_pad, np.int64)[None, None], coeff.shape)
+    b, c = np.meshgrid(np.arange(X.shape[0]), np.arange(X.shape[1]), indexing="ij")
+    np.add.at(dX, (b[:, :, None, None], c[:, :, None, None], idx), coeff * G[:, :, None, :])
+    return dX[:, :, :n_in].astype(f32)
+
+
 def knn_norm(X, mode, weight=None, bias=None, eps=1e-5, groups=1):
     """Per-sample norms of [B,C,N] activations (fovi/arch/norm.py:14-101 = torch LayerNorm / GroupNorm, biased variance):
     'channel' over C, 'coord' over N, 'layer' over (C, N), 'group' over (C/groups, N).  weight / bias broadcast as torch

@@ -290,10 +290,35 @@ def norms_fixture(save, knn):
     print("norms fixture: groups", int(out["group_groups"]), "pool n_in", len(ic), "n_out", len(oc))
 
 
+def pool_backward_fixture(save, knn):
+    """Gradients of the reference's KNNPoolingLayer (fovi/arch/knn.py:345-394) with respect to its input, from its own
+    autograd on CPU in float32, for the four pooling modes on a small strided sensor pair (pad neighbours at the rim)."""
+    rs = np.random.RandomState(71)
+    ic, oc, _ = knn.get_in_out_coords(24, 16, 1.0, 2, style="isotropic", auto_match_cart_resources=0, device="cpu")
+    x = rs.standard_normal((2, 5, len(ic))).astype(f32)
+    out = {"seed": np.int64(71), "x": x, "n_in": np.int64(len(ic))}
+    with torch.enable_grad():
+        for mode in ("max", "avg", "sum", "gaussian"):
+            pool = knn.KNNPoolingLayer(9, ic, oc, mode=mode, device="cpu", gauss_sigma=0.6)
+            xt = torch.from_numpy(x).requires_grad_(True)
+            y = pool(xt)
+            gy = torch.from_numpy(rs.standard_normal(tuple(y.shape)).astype(f32))
+            y.backward(gy)
+            out[f"{mode}_gy"], out[f"{mode}_dx"], out[f"{mode}_y"] = gy.numpy(), xt.grad.numpy(), y.detach().numpy()
+            if mode == "gaussian":
+                out["weights"] = pool.gaussian_weights.numpy()
+        out["knn_idx_pad"] = pool.knn_indices_pad_token.numpy().astype(np.int32)
+        out["knn_idx"] = pool.knn_indices.numpy().astype(np.int32)
+        out["distances"] = pool.knn_distances.numpy()
+    n_pad = int((out["knn_idx_pad"] == len(ic)).sum())
+    save("pool_backward_small.npz", **out)
+    print("pool backward fixture: n_in", len(ic), "n_out", len(oc), "pad entries", n_pad)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
-    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise", "norms", "sampler_backward"], help="regenerate one fixture group only")
+    ap.add_argument("--only", default=None, choices=[None, "alexnet", "backward", "depthwise", "norms", "sampler_backward", "pool_backward"], help="regenerate one fixture group only")
     args = ap.parse_args()
     knn, retina, coords, knnvit = load_reference(args.reference)
     torch.set_grad_enabled(False)
@@ -308,6 +333,8 @@ def main():
         return norms_fixture(save, knn)
     if args.only == "sampler_backward":
         return sampler_backward_fixture(save, retina)
+    if args.only == "pool_backward":
+        return pool_backward_fixture(save, knn)
 
     # ------------------------------------------------------------ sensors (geometry fixtures)
     sensors = {}
@@ -478,6 +505,7 @@ def main():
     depthwise_fixture(save, knn)
     norms_fixture(save, knn)
     sampler_backward_fixture(save, retina)
+    pool_backward_fixture(save, knn)
 
 
 if __name__ == "__main__":

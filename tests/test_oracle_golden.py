@@ -169,3 +169,11 @@ def test_norms_and_gaussian_pooling_oracle(golden):
         assert np.abs(o - g[f"{name}_out"]).max() < 2e-6, name
     o = oracle.knn_pool_weighted(g["pool_x"], g["pool_knn_idx_pad"], g["pool_weights"])
     assert np.allclose(o, g["pool_out"], rtol=1e-5, atol=1e-6, equal_nan=True)
+
+
+@pytest.mark.parametrize("mode", ["max", "avg", "sum", "gaussian"])
+def test_pool_backward_oracle_matches_reference_autograd(golden, mode):
+    """oracle.knn_pool_backward against the gradients the reference's own autograd produced (fovi/arch/knn.py:345-394)."""
+    g = golden("pool_backward_small.npz")
+    dx = oracle.knn_pool_backward(g["x"], g["knn_idx_pad"], g[f"{mode}_gy"], mode, g["weights"] if mode == "gaussian" else None)
+    assert np.abs(dx - g[f"{mode}_dx"]).max() < 1e-5
