@@ -101,9 +101,30 @@ class KNNAlexNetBlock(nn.Module):
             h = self.pool.forward_points(h)
         return h
 
-    @torch.no_grad()
+    def _wants_grad(self, x):
+        return torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters()))
+
+    def _forward_train(self, x):
+        """The block under autograd: the convolution's own gradients (fovi_b200/grad.py), torch's norm and activation as in
+        the reference (batch norm with batch statistics in training mode), the pooling's own gradient."""
+        if self.conv is not None:
+            x = self.conv(x)
+        if self.norm is not None:
+            x = self.norm(x)
+        if self.activation is not None:
+            x = self.activation(x)
+        if self.pool is not None:
+            x = self.pool(x)
+        return x
+
     def forward(self, x):
         """x [B, C_in, N_in] -> [B, C_out, N_out] (fovi/arch/knnalexnet.py:109-127)."""
+        if self._wants_grad(x):
+            return self._forward_train(x)
+        with torch.no_grad():
+            return self._forward_eval(x)
+
+    def _forward_eval(self, x):
         if self.points_path:
             h = self.forward_points(ops.pack_points(x, self.conv.plan), x.shape[0])
             return h.permute(0, 2, 1).to(x.dtype)
@@ -164,9 +185,19 @@ class KNNAlexNet(nn.Module):
             h = L.forward_points(h, rows) if isinstance(L, KNNAlexNetBlock) else L.forward_points(h)
         return h
 
-    @torch.no_grad()
     def forward(self, x):
-        """x [B, C_in, N_in] -> logits [B, n_classes], or features [B, C_out, N_out] without a classifier."""
+        """x [B, C_in, N_in] -> logits [B, n_classes], or features [B, C_out, N_out] without a classifier.  Under autograd
+        (training) the blocks run one by one with gradients; otherwise on the kernels' channels-last path."""
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            for L in self.layers:
+                x = L(x)
+            if self.n_classes is not None:
+                x = self.classifier(x.reshape(x.shape[0], -1))
+            return x
+        with torch.no_grad():
+            return self._forward_eval(x)
+
+    def _forward_eval(self, x):
         if self.points_path:
             h = self.forward_points(ops.pack_points(x, self.layers[0].conv.plan), x.shape[0])
             x = h.permute(0, 2, 1).to(x.dtype)

@@ -2,7 +2,9 @@
 same class names, constructor signatures and parameter names/shapes (they subclass the same torch modules, so state
 dicts line up).  Batch norm (every shipped configuration) is folded into the convolution by ``KNNAlexNetBlock``; the
 per-sample norms (channel / coord / layer / group) run on the CUDA normalisation kernels, on both activation layouts,
-with the following ReLU fused.  Inference only: under autograd they fall back to nothing — they raise.
+with the following ReLU fused.  Under autograd (training) the per-sample norms are evaluated with the torch functions
+the reference's own layers call (``F.layer_norm`` / ``F.group_norm`` on the same axes), which carry the gradients; batch
+norm in training mode is torch's ``BatchNorm1d`` as in the reference.
 """
 import numpy as np
 import torch
@@ -22,10 +24,22 @@ class _KernelNorm:
 
     def _run(self, x, layout, relu=False, out_dtype=None):
         if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
-            raise RuntimeError(f"{self.__class__.__name__} implements the forward pass only: call it under torch.no_grad()")
+            y = self._torch_forward(x if layout == ops.ACT_BCN else x.permute(0, 2, 1))      # [B, C, N] view
+            y = torch.relu(y) if relu else y
+            y = y if layout == ops.ACT_BCN else y.permute(0, 2, 1)
+            return y if out_dtype is None else y.to(out_dtype)
         w = self.weight.reshape(-1) if self.weight is not None else None
         b = self.bias.reshape(-1) if self.bias is not None else None
         return ops.knn_norm(x, self._mode, w, b, eps=self.eps, groups=self._groups(), layout=layout, relu=relu, out_dtype=out_dtype)
+
+    def _torch_forward(self, x):
+        """Differentiable evaluation on [B, C, N] with the reference's torch calls (fovi/arch/norm.py:14-101)."""
+        import torch.nn.functional as F
+        if self._mode == "channel":
+            return F.layer_norm(x.transpose(1, 2), self.normalized_shape, self.weight, self.bias, self.eps).transpose(1, 2)
+        if self._mode in ("coord", "layer"):
+            return F.layer_norm(x, self.normalized_shape, self.weight, self.bias, self.eps)
+        return F.group_norm(x, self.num_groups, self.weight, self.bias, self.eps)
 
     def forward(self, x):
         return self._run(x, ops.ACT_BCN)

@@ -121,3 +121,73 @@ def test_foveated_alexnet_equals_sampler_then_network(net):
     # the fused route rounds the sensor output to bf16 exactly as pack_points does, so the two agree to rounding of the classifier
     assert rel_l2(per_fix.cpu().numpy(), ref.float().cpu().numpy()) < 1e-3
     np.testing.assert_allclose(model(img, fix, fix_agg="mean").cpu().numpy(), per_fix.mean(1).cpu().numpy(), rtol=1e-6, atol=1e-6)
+
+
+def _torch_block(x, conv, norm, pool, P, prefix):
+    """The reference's formulation of one block in float32 torch ops (gather + tap-indexed weights + linear map,
+    fovi/arch/knn.py:484-557; BatchNorm1d with batch statistics; ReLU; nan-aware pooling, knn.py:345-371) on the parameter
+    tensors P[prefix + ...]."""
+    import torch.nn.functional as F
+    idx = conv.knn_indices_pad_token.to(x.device)                       # [K, n_out], pad == n_in
+    tap = conv.tap.to(x.device)                                          # [n_out, K]
+    V = conv.ref_coords.shape[0]
+    co, ci = conv.out_channels, conv.in_channels
+    xp = torch.cat([x, torch.zeros_like(x[:, :, :1])], 2)
+    g = xp[:, :, idx]                                                    # [B, ci, K, n_out]
+    w = P[prefix + "conv.weight"].view(co, ci, V)[:, :, tap]             # [co, ci, n_out, K]
+    y = torch.einsum("bckn,ocnk->bon", g, w)
+    if prefix + "conv.bias" in P:
+        y = y + P[prefix + "conv.bias"][None, :, None]
+    if norm is not None:
+        y = F.batch_norm(y, None, None, P[prefix + "norm.weight"], P[prefix + "norm.bias"], True, 0.0, norm.eps)
+    y = torch.relu(y)
+    if pool is not None:
+        pidx = pool.knn_indices_pad_token.to(x.device)
+        yp = torch.cat([y, torch.full_like(y[:, :, :1], float("nan"))], 2)[:, :, pidx]     # [B, C, K, n_out]
+        yp = torch.where(torch.isnan(yp), torch.full_like(yp, -float("inf")), yp)
+        y = yp.max(2).values
+    return y
+
+
+@pytest.mark.autograd
+def test_network_trains_with_batch_statistics():
+    """KNNAlexNet in training mode: convolution gradients from the tensor-core kernels, batch norm with batch statistics,
+    max pooling with its own gradient; the first step's gradients against torch autograd through the reference's
+    formulation of the same network, and a few optimizer steps reduce the loss."""
+    from fovi_b200.alexnet import KNNAlexNet
+    torch.manual_seed(0)
+    net = KNNAlexNet(in_res=24, in_channels=3, features_per_layer=[16, 32], stride_per_layer=[2, 1], pool_after=[0], k_per_layer=[9, 9],
+                     n_classes=5, out_res=None, auto_match_cart_resources=0, fov=16.0, cmf_a=1.0, norm_type="batch", device="cuda").train()
+    n0 = net.layers[0].in_coords.shape[0]
+    x = torch.randn(12, 3, n0, device="cuda")
+    target = torch.randint(0, 5, (12,), device="cuda")
+    P = {n: p.detach().clone().float().requires_grad_(True) for n, p in net.named_parameters()}
+
+    def ref_forward():
+        h = x
+        for i, blk in enumerate(net.layers):
+            h = _torch_block(h, blk.conv, blk.norm, blk.pool, P, f"layers.{i}.")
+        return torch.nn.functional.linear(h.reshape(h.shape[0], -1), P["classifier.weight"], P["classifier.bias"])
+
+    loss = torch.nn.functional.cross_entropy(net(x), target)
+    loss.backward()
+    loss_ref = torch.nn.functional.cross_entropy(ref_forward(), target)
+    loss_ref.backward()
+    assert abs(loss.item() - loss_ref.item()) < 2e-2 * max(1.0, abs(loss_ref.item()))
+    for name, p in net.named_parameters():
+        q = P[name]
+        assert p.grad is not None and torch.isfinite(p.grad).all(), name
+        err = float((p.grad.float() - q.grad).norm() / q.grad.norm().clamp_min(1e-12))
+        assert err < 1e-1, (name, err)     # bf16 activations through batch norm and a max pool, whose argmax can switch under bf16 rounding
+    opt = torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9)
+    first = None
+    for _ in range(8):
+        opt.zero_grad()
+        loss = torch.nn.functional.cross_entropy(net(x), target)
+        loss.backward()
+        opt.step()
+        first = loss.item() if first is None else first
+    assert loss.item() < 0.7 * first
+    net.eval()
+    with torch.no_grad():
+        assert net(x).shape == (12, 5)       # the inference path (folded running statistics) still runs after training

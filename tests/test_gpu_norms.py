@@ -33,8 +33,13 @@ def test_norm_layers_match_reference(golden):
             ref = np.maximum(ref, 0)
             got = yp.float().permute(0, 2, 1).cpu().numpy()
             assert yp.dtype == torch.bfloat16 and np.abs(got - ref).max() < 2e-2 * max(1.0, np.abs(ref).max()), name
-        with torch.enable_grad(), pytest.raises(RuntimeError):
-            layer(xd)
+        with torch.enable_grad():          # under autograd: the reference's torch calls, same numbers, with gradients
+            xg = xd.clone().requires_grad_(True)
+            yg = layer(xg)
+            assert yg.grad_fn is not None and np.abs(yg.detach().cpu().numpy() - g[f"{name}_out"]).max() < 1e-5, name
+            yg.square().sum().backward()
+            assert xg.grad is not None and layer.weight.grad is not None and torch.isfinite(xg.grad).all()
+            layer.weight.grad = layer.bias.grad = None
     assert norm.find_valid_num_groups(24, 32) == 6 and norm.find_valid_num_groups(96, 32) == 24 and norm.find_valid_num_groups(7, 32) == 1
     assert isinstance(norm.get_norm("layer_chan", N, C), norm.KNNChannelNorm) and isinstance(norm.get_norm("force_batch", N, C), norm.KNNBatchNorm)
     assert norm.get_norm("none", N, C) is None
