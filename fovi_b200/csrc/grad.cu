@@ -40,73 +40,86 @@ __global__ void batch_to_inner_kernel(const T* __restrict__ src, __nv_bfloat16* 
 // gradient is also written back in the source layout (`masked`, for the input-gradient GEMM) and its sums over
 // everything but the fast index (the channels: the bias gradient) are added into `colsum` -- one read of the gradient
 // instead of three.
+constexpr int X2_SLOW = 4;   // consecutive values of the slow index one block works through
+
 template <typename T, bool FAST_I>
 __global__ void __launch_bounds__(256) batch_to_inner_x2_kernel(const T* __restrict__ src, __nv_bfloat16* __restrict__ dst, int B, int I, int J,
                                                                int Jp, int Bp, long long sb, long long si, long long sj,
                                                                const T* __restrict__ act, T* __restrict__ masked, float* __restrict__ colsum) {
   __shared__ __nv_bfloat16 tile[64][66];
   __shared__ float part[8][64];
-  const int b0 = blockIdx.x * 64, f0 = blockIdx.y * 64, slow = blockIdx.z;
-  const int F = FAST_I ? I : J;
+  const int b0 = blockIdx.x * 64, f0 = blockIdx.y * 64;
+  const int F = FAST_I ? I : J, n_slow = FAST_I ? Jp : I;
   const int tx = threadIdx.x, ty = threadIdx.y;
   float s0 = 0.f, s1 = 0.f;
-  for (int r = ty; r < 64; r += 8) {
-    const int b = b0 + r, f = f0 + 2 * tx;
-    const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
-    float v0 = 0.f, v1 = 0.f;
-    if (b < B && f < F && j < J) {   // F is even: f + 1 < F as well
-      const long long off = b * sb + i * si + j * sj;
-      const T* p = src + off;
-      if (sizeof(T) == 2) {
-        const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(p);
-        v0 = __bfloat162float(q.x); v1 = __bfloat162float(q.y);
-      } else {
-        const float2 q = *reinterpret_cast<const float2*>(p);
-        v0 = q.x; v1 = q.y;
-      }
-      if (act) {
-        float a0, a1;
-        if (sizeof(T) == 2) {
-          const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(act + off);
-          a0 = __bfloat162float(q.x); a1 = __bfloat162float(q.y);
-        } else {
-          const float2 q = *reinterpret_cast<const float2*>(act + off);
-          a0 = q.x; a1 = q.y;
-        }
-        v0 = a0 > 0.f ? v0 : 0.f; v1 = a1 > 0.f ? v1 : 0.f;
-      }
-      if (masked) {
-        if (sizeof(T) == 2) {
-          __nv_bfloat162 q;
-          q.x = __float2bfloat16_rn(v0); q.y = __float2bfloat16_rn(v1);
-          *reinterpret_cast<__nv_bfloat162*>(masked + off) = q;
-        } else {
-          *reinterpret_cast<float2*>(masked + off) = make_float2(v0, v1);
-        }
-      }
-      s0 += v0; s1 += v1;
-    }
-    tile[r][2 * tx] = __float2bfloat16_rn(v0);
-    tile[r][2 * tx + 1] = __float2bfloat16_rn(v1);
-  }
-  if (colsum) { part[ty][2 * tx] = s0; part[ty][2 * tx + 1] = s1; }
-  __syncthreads();
-  if (colsum && ty == 0) {
-    for (int e = 0; e < 2; ++e) {
-      float t = 0.f;
-      for (int w = 0; w < 8; ++w) t += part[w][2 * tx + e];
-      const int f = f0 + 2 * tx + e;
-      if (f < F) atomicAdd(colsum + f, t);
-    }
-  }
-  const int Fd = FAST_I ? I : Jp;
-  for (int r = ty; r < 64; r += 8) {
-    const int f = f0 + r, b = b0 + 2 * tx;
-    if (f < Fd && b < Bp) {          // Bp is even
+  for (int sl = 0; sl < X2_SLOW; ++sl) {
+    const int slow = blockIdx.z * X2_SLOW + sl;
+    if (slow >= n_slow) break;           // uniform over the block
+    if (sl) __syncthreads();             // the tile is free again
+    for (int r = ty; r < 64; r += 8) {
+      const int b = b0 + r, f = f0 + 2 * tx;
       const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
-      __nv_bfloat162 q;
-      q.x = tile[2 * tx][r]; q.y = tile[2 * tx + 1][r];
-      *reinterpret_cast<__nv_bfloat162*>(dst + ((long long)i * Jp + j) * Bp + b) = q;
+      float v0 = 0.f, v1 = 0.f;
+      if (b < B && f < F && j < J) {   // F is even: f + 1 < F as well
+        const long long off = b * sb + i * si + j * sj;
+        const T* p = src + off;
+        if (sizeof(T) == 2) {
+          const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(p);
+          v0 = __bfloat162float(q.x); v1 = __bfloat162float(q.y);
+        } else {
+          const float2 q = *reinterpret_cast<const float2*>(p);
+          v0 = q.x; v1 = q.y;
+        }
+        if (act) {
+          float a0, a1;
+          if (sizeof(T) == 2) {
+            const __nv_bfloat162 q = *reinterpret_cast<const __nv_bfloat162*>(act + off);
+            a0 = __bfloat162float(q.x); a1 = __bfloat162float(q.y);
+          } else {
+            const float2 q = *reinterpret_cast<const float2*>(act + off);
+            a0 = q.x; a1 = q.y;
+          }
+          v0 = a0 > 0.f ? v0 : 0.f; v1 = a1 > 0.f ? v1 : 0.f;
+        }
+        if (masked) {
+          if (sizeof(T) == 2) {
+            __nv_bfloat162 q;
+            q.x = __float2bfloat16_rn(v0); q.y = __float2bfloat16_rn(v1);
+            *reinterpret_cast<__nv_bfloat162*>(masked + off) = q;
+          } else {
+            *reinterpret_cast<float2*>(masked + off) = make_float2(v0, v1);
+          }
+        }
+        s0 += v0; s1 += v1;
+      }
+      __nv_bfloat162 t2;
+      t2.x = __float2bfloat16_rn(v0); t2.y = __float2bfloat16_rn(v1);
+      *reinterpret_cast<__nv_bfloat162*>(&tile[r][2 * tx]) = t2;
+    }
+    __syncthreads();
+    const int Fd = FAST_I ? I : Jp;
+    for (int r = ty; r < 64; r += 8) {
+      const int f = f0 + r, b = b0 + 2 * tx;
+      if (f < Fd && b < Bp) {          // Bp is even
+        const int i = FAST_I ? f : slow, j = FAST_I ? slow : f;
+        __nv_bfloat162 q;
+        q.x = tile[2 * tx][r]; q.y = tile[2 * tx + 1][r];
+        *reinterpret_cast<__nv_bfloat162*>(dst + ((long long)i * Jp + j) * Bp + b) = q;
+      }
+    }
+  }
+  if (colsum) {
+    // in the FAST_I == false orientation the fast index (the channel) is the same for every slow index of the block, and in
+    // the FAST_I orientation too: the sums of all X2_SLOW passes belong to the same 64 channels
+    part[ty][2 * tx] = s0; part[ty][2 * tx + 1] = s1;
+    __syncthreads();
+    if (ty == 0) {
+      for (int e = 0; e < 2; ++e) {
+        float t = 0.f;
+        for (int w = 0; w < 8; ++w) t += part[w][2 * tx + e];
+        const int f = f0 + 2 * tx + e;
+        if (f < F) atomicAdd(colsum + f, t);
+      }
     }
   }
 }
@@ -219,7 +232,7 @@ static int batch_to_inner_impl(const void* src, int dtype, int B, int I, int J, 
     if (colsum) FOVI_CUDA(cudaMemsetAsync(colsum, 0, sizeof(float) * (size_t)F, st));
   }
   if (x2) {
-    dim3 grid2((Bp + 63) / 64, (fast + 63) / 64, slow), block2(32, 8);
+    dim3 grid2((Bp + 63) / 64, (fast + 63) / 64, (slow + X2_SLOW - 1) / X2_SLOW), block2(32, 8);
 #define RUN2(T, FI) batch_to_inner_x2_kernel<T, FI><<<grid2, block2, 0, st>>>((const T*)src, (__nv_bfloat16*)dst, B, I, J, Jp, Bp, sb, si, sj, \
                                                                               (const T*)act, (T*)masked, colsum)
     if (dtype == FOVI_F32) { if (fast_i) RUN2(float, true); else RUN2(float, false); }
