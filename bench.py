@@ -33,7 +33,7 @@ CHANS = [3, 64, 192, 384, 256, 256]
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload (256 images x 4 fixations,
 # captured directly: three metrics, one pass); sampler, then the five KNNConv launches.  `sources` is the hash of the kernel
 # sources the capture was taken on: when the sources change the figure is reported as null until the capture is redone.
-NCU_DRAM_TRAFFIC_MB = {"workload": (256, 4), "sources": "164c524a8a84e281", "sampler": 207.9, "conv": [220.5, 197.1, 226.1, 285.5, 207.1]}
+NCU_DRAM_TRAFFIC_MB = {"workload": (256, 4), "sources": "755e5d3a984b21c1", "sampler": 208.1, "conv": [220.2, 196.7, 225.7, 284.3, 207.0]}
 METRIC = "images x fixations/s through sensor+KNNConv"
 UNIT = "img*fix/s"
 
