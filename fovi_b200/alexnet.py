@@ -2,11 +2,13 @@
 ``KNNAlexNet`` (fovi/arch/knnalexnet.py:13-127, 130-260) with the same constructor signatures, sub-module names
 (``layers.{i}.conv / .norm / .pool``, ``classifier``) and parameter shapes, so reference checkpoints load unchanged.
 
-Inference only.  A block is conv -> norm -> activation -> pool; here batch normalisation (the norm of every shipped
-configuration, fovi/arch/norm.py:36-48, evaluated with its running statistics) is folded into the convolution's packed
-weights and bias and ReLU runs in the convolution's epilogue; a per-sample norm (channel / coord / layer / group) runs
-as its own kernel behind the convolution with the ReLU fused into it; pooling is the gather-reduce kernel on the same
-channels-last layout, so activations stay in the kernels' layout from the sensor to the classifier.
+A block is conv -> norm -> activation -> pool.  Without gradients (inference) batch normalisation (the norm of every
+shipped configuration, fovi/arch/norm.py:36-48, evaluated with its running statistics) is folded into the convolution's
+packed weights and bias and ReLU runs in the convolution's epilogue; a per-sample norm (channel / coord / layer / group)
+runs as its own kernel behind the convolution with the ReLU fused into it; pooling is the gather-reduce kernel on the same
+channels-last layout, so activations stay in the kernels' layout from the sensor to the classifier.  Under autograd
+(training) the blocks run one by one: the convolution and the pooling with their own gradient kernels, the norm and the
+activation through torch as in the reference (batch norm with batch statistics in training mode).
 """
 import numpy as np
 import torch
